@@ -1,0 +1,197 @@
+/* cake_b200.h -- C ABI of the B200 (sm_100a) native target for open-cake-ir's inference
+ * workload contracts.
+ *
+ * Every operator follows the host ABI of the reference's native CUDA backend
+ * (corpus/expected/native-gemm-bias.txt:170-215, consumed by
+ * tools/native_cuda_evaluate.py:485-520 and described in docs/NATIVE_CUDA_DESIGN.md:98-104):
+ *
+ *     int <op>_create (void** buffers, <config>, void** handle_out);
+ *     int <op>_launch (void* handle, void* cuda_stream);
+ *     int <op>_destroy(void* handle);
+ *
+ * `buffers` holds DEVICE pointers in the order of the workload contract's tensor ABI
+ * (inputs, then outputs; src/open_cake_ir/evaluation/workload.py:147-190), followed where an
+ * operator needs scratch by a caller-owned workspace pointer.  All tensors are contiguous
+ * row-major.  The caller owns every buffer, the stream and all synchronisation; `create`
+ * validates, records pointers, encodes tensor maps and sets function attributes -- it does
+ * not allocate device memory, copy or launch.  `launch` only enqueues kernels on the given
+ * stream.  Inputs are never written.  A handle must outlive the launches queued from it and
+ * must be used on the device that was current at `create`.
+ *
+ * Two things the reference ABI does not have, added because these kernels are not
+ * shape-specialised source: a per-operator config struct passed to `create` (the reference
+ * bakes shapes into emitted code), and a device status word at the start of the workspace
+ * that a kernel sets when one of its bounded waits runs out (read it with
+ * cake_b200_read_status after synchronising the stream).
+ *
+ * Return values: 0 on success; a cudaError_t value; 10000 + CUresult for driver errors
+ * (the reference's convention, native-gemm-bias.txt:192,199); 20001.. for this library's
+ * own argument errors (see CAKE_B200_ERR_*).  No exceptions, no aborts, no internal threads.
+ */
+#ifndef CAKE_B200_H
+#define CAKE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CAKE_B200_ERR_BAD_ARGUMENT 20001
+#define CAKE_B200_ERR_WRONG_DEVICE 20002
+#define CAKE_B200_ERR_NOT_BLACKWELL 20003
+#define CAKE_B200_ERR_WORKSPACE 20004
+#define CAKE_B200_ERR_DEVICE_STATUS 20005
+
+/* Library identification: ABI version (bumped on any incompatible change). */
+int cake_b200_abi_version(void);
+
+/* Copies the 4-byte status word at the start of `workspace` to the host (synchronous on
+ * `cuda_stream`).  0 = every kernel ran to completion; otherwise the code of the first wait
+ * that gave up (1 smem-full, 2 smem-empty, 3 tmem-full, 4 tmem-empty, 5 flag). */
+int cake_b200_read_status(const void* workspace, void* cuda_stream, int* status_out);
+
+/* ------------------------------------------------------------------------------------------
+ * RMSNorm.  Replaces the emitted RMSNorm starter (src/open_cake_ir/tasks/solx_fib/authoring.py:9-53)
+ * for the operator defined at src/open_cake_ir/tasks/solx_fib/workload.py:214-218, :334-358:
+ *   out[r,c] = bf16( z[r,c] * weight[c] / sqrt(mean_j z[r,j]^2 + epsilon) ),  z = x  or  fp32(x + residual)
+ * buffers: x bf16 [rows,width], (residual bf16 [rows,width] if fused_residual), weight bf16 [width],
+ *          out bf16 [rows,width].  width must be a multiple of 8.  No workspace.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t rows;
+  int64_t width;
+  float epsilon;
+  int32_t fused_residual; /* 0: x only; 1: buffers = x, residual, weight, out */
+} cake_b200_rmsnorm_config;
+int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_config* config, void** handle_out);
+int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream);
+int cake_b200_rmsnorm_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * Block-scaled FP8 GEMM.  Replaces the emitted block-scaled GEMM
+ * (corpus/schedules/block-scaled-gemm-b1-smoke.json, golden corpus/expected/block-scaled-gemm-accepted.txt;
+ * oracle tools/kernel_oracles.py:98-112):
+ *   c[m,n] = bf16( sum_k a[m,k]*sfa[k/128,m] * b[n,k]*sfb[n/128,k/128] ), fp32 accumulation
+ * buffers: a e4m3 [M,K], sfa fp32 [K/128,M], b e4m3 [N,K], sfb fp32 [N/128,K/128], c bf16 [M,N],
+ *          workspace (>= cake_b200_block_scaled_gemm_workspace_bytes).  K % 128 == 0, N % 256 == 0.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t m, n, k;
+} cake_b200_gemm_config;
+size_t cake_b200_block_scaled_gemm_workspace_bytes(const cake_b200_gemm_config* config);
+int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b200_gemm_config* config, void** handle_out);
+int cake_b200_block_scaled_gemm_launch(void* handle, void* cuda_stream);
+int cake_b200_block_scaled_gemm_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * MoE routing.  Replaces the four routing stages of the reference launch plan
+ * (src/open_cake_ir/tasks/solx_fib/moe.py:167-215; oracle moe.py:275-287; top-k key order
+ * compiler/backends/triton.py:2428-2460).
+ *   mode 0 (DeepSeek-V3): s = sigmoid(logits); choice by s + bias; group score = sum of the two best of each
+ *     group; best `topk_group` groups; best `top_k` experts inside them; weights = s[sel] / (sum s[sel] + 1e-20) * factor.
+ *   mode 1 (softmax top-k): best `top_k` raw logits; weights = softmax over the selected logits * factor.
+ *   Ties go to the lower index; results are in descending score order.
+ * buffers: routing_logits fp32 [T,E], routing_bias bf16 [E], routed_scaling_factor fp32 [1],
+ *          expert_ids int32 [T,top_k], route_weights fp32 [T,top_k].  E <= 512 and E % 32 == 0.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t tokens;
+  int32_t experts, top_k, n_group, topk_group;
+  int32_t mode; /* 0 = DeepSeek-V3 group-limited sigmoid, 1 = softmax over the selected top-k */
+} cake_b200_routing_config;
+int cake_b200_moe_routing_create(void** buffers, const cake_b200_routing_config* config, void** handle_out);
+int cake_b200_moe_routing_launch(void* handle, void* cuda_stream);
+int cake_b200_moe_routing_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * Token permute.  Fixes the order the reference leaves open (atomic reservation judged by ownership,
+ * tools/kernel_oracles.py:186-190; padded gather :137-156): routed (token, slot) pairs whose expert is in
+ * [local_expert_offset, +local_experts) are stably sorted by expert.
+ * buffers: expert_ids int32 [T,top_k], local_expert_offset int32 [1],
+ *          counts int32 [local_experts], offsets int32 [local_experts+1], sorted_pairs int32 [T*top_k],
+ *          inv_perm int32 [T*top_k] (-1 for pairs of other ranks).  No workspace.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t tokens;
+  int32_t top_k, local_experts;
+} cake_b200_permute_config;
+int cake_b200_moe_permute_create(void** buffers, const cake_b200_permute_config* config, void** handle_out);
+int cake_b200_moe_permute_launch(void* handle, void* cuda_stream);
+int cake_b200_moe_permute_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * FP8 block-scaled MoE expert layer (rank-local).  Replaces the eight-stage launch plan
+ * src/open_cake_ir/tasks/solx_fib/moe.py:158-268 for the operator whose oracle is moe.py:122-155:
+ * routing -> permute -> grouped GEMM1 (e4m3 x e4m3, fp32 block scales) + SwiGLU (silu on the second half)
+ * -> grouped GEMM2 * route weight -> sum over slots -> bf16.
+ * buffers (the contract's order, moe.py:13-20): routing_logits fp32 [T,E], routing_bias bf16 [E],
+ *   hidden_states e4m3 [T,H], hidden_states_scale fp32 [H/128,T], gemm1_weights e4m3 [E_local,2I,H],
+ *   gemm1_weights_scale fp32 [E_local,2I/128,H/128], gemm2_weights e4m3 [E_local,H,I],
+ *   gemm2_weights_scale fp32 [E_local,H/128,I/128], local_expert_offset int32 [1],
+ *   routed_scaling_factor fp32 [1], output bf16 [T,H], workspace (>= cake_b200_moe_workspace_bytes).
+ * act_mode: 0 = intermediate activation requantised to e4m3 per (row,128) with amax/448 scales (one FP8 term);
+ *           1 = two FP8 terms (value + residual), which carries the intermediate at better than bf16
+ *               precision and meets the reference contract's tolerance against its unquantised oracle.
+ * H % 256 == 0, I % 128 == 0.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t tokens;
+  int32_t hidden, intermediate;
+  int32_t experts, local_experts, top_k, n_group, topk_group;
+  int32_t routing_mode; /* as cake_b200_routing_config.mode */
+  int32_t act_mode;
+  int32_t external_routing; /* 1: buffers[0], buffers[1] are expert_ids int32 [T,top_k] and route_weights fp32
+                               [T,top_k] produced elsewhere (e.g. after an expert-parallel dispatch); routing is skipped */
+} cake_b200_moe_config;
+size_t cake_b200_moe_workspace_bytes(const cake_b200_moe_config* config);
+int cake_b200_moe_create(void** buffers, const cake_b200_moe_config* config, void** handle_out);
+int cake_b200_moe_launch(void* handle, void* cuda_stream);
+int cake_b200_moe_destroy(void* handle);
+/* Device pointers of intermediates inside the workspace, for tests and for expert-parallel callers:
+ * which = 0 expert_ids int32 [T,top_k]; 1 route_weights fp32 [T,top_k]; 2 counts; 3 offsets; 4 sorted_pairs; 5 inv_perm. */
+int cake_b200_moe_intermediate(void* handle, int which, void** device_pointer_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Paged GQA decode.  Replaces the four-stage attention launch plan
+ * src/open_cake_ir/tasks/solx_fib/attention.py:190-331 for the decode operator whose oracle is
+ * attention.py:132-183 (spec attention_specs.py:44-84): one query token per sequence,
+ *   out = bf16(softmax(K q * sm_scale) V), lse = logsumexp / ln 2 (base 2, -inf and zero output for an empty sequence).
+ * buffers: q bf16 [B,Hq,D], k_cache bf16 [pages,page_size,Hkv,D], v_cache (same), kv_indptr int32 [B+1] (pages),
+ *          kv_indices int32 [*], kv_last_page_len int32 [B] (extension for page_size > 1; the reference has page_size 1),
+ *          sm_scale fp32 [1], output bf16 [B,Hq,D], lse fp32 [B,Hq], workspace.  D == 128; Hq/Hkv in {1,2,4,8}.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t batch;
+  int32_t num_qo_heads, num_kv_heads, head_dim, page_size;
+  int64_t max_kv_len; /* upper bound of any sequence's length, used only to size the split-KV schedule */
+} cake_b200_gqa_decode_config;
+size_t cake_b200_gqa_decode_workspace_bytes(const cake_b200_gqa_decode_config* config);
+int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_decode_config* config, void** handle_out);
+int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream);
+int cake_b200_gqa_decode_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * Paged MLA decode (absorbed form).  Same launch plan and oracle as above, MLA branch
+ * (attention.py:164-165, :175-177; spec attention_specs.py:249-292):
+ *   logits = (ckv . q_nope + kpe . q_pe) * sm_scale; out = bf16(softmax(logits) ckv); lse base 2.
+ * buffers: q_nope bf16 [B,H,512], q_pe bf16 [B,H,64], ckv_cache bf16 [pages,page_size,512],
+ *          kpe_cache bf16 [pages,page_size,64], kv_indptr int32 [B+1], kv_indices int32 [*],
+ *          kv_last_page_len int32 [B], sm_scale fp32 [1], output bf16 [B,H,512], lse fp32 [B,H], workspace.
+ *          H % 16 == 0.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t batch;
+  int32_t num_qo_heads, head_dim_ckv, head_dim_kpe, page_size;
+  int64_t max_kv_len;
+} cake_b200_mla_decode_config;
+size_t cake_b200_mla_decode_workspace_bytes(const cake_b200_mla_decode_config* config);
+int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_decode_config* config, void** handle_out);
+int cake_b200_mla_decode_launch(void* handle, void* cuda_stream);
+int cake_b200_mla_decode_destroy(void* handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAKE_B200_H */

@@ -1,0 +1,16 @@
+"""B200 (sm_100a) native target for open-cake-ir's inference workload contracts.
+
+The product is ``libcake_b200.so`` -- hand-written CUDA behind a C ABI (``include/cake_b200.h``).
+This package is the Python host side a user of the reference calls instead of the reference's
+emitted Triton launch plans: the same operators, tensor names, layouts, dtypes and scale
+conventions (``operators``), thin ctypes bindings (``_lib``), the operator objects that own a
+native handle (``ops``) and seeded synthetic inputs at serving shapes (``workloads``).
+There is no CPU fallback: every operator raises if the native library is missing.
+"""
+from . import _lib, operators, ops, workloads  # noqa: F401
+from .ops import (BlockScaledGemm, Fp8Moe, GqaPagedDecode, MlaPagedDecode, MoePermute, MoeRouting, RmsNorm,
+                  block_scaled_gemm, fp8_moe, gqa_paged_decode, mla_paged_decode, moe_permute, moe_routing, rmsnorm)
+
+__all__ = ["BlockScaledGemm", "Fp8Moe", "GqaPagedDecode", "MlaPagedDecode", "MoePermute", "MoeRouting", "RmsNorm",
+           "block_scaled_gemm", "fp8_moe", "gqa_paged_decode", "mla_paged_decode", "moe_permute", "moe_routing",
+           "rmsnorm", "operators", "ops", "workloads"]
