@@ -1,0 +1,414 @@
+"""Benchmark of the hot path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line.  A step is one pass of
+the FP8 block-scaled MoE expert layer at the DeepSeek-V3 shape (4096 tokens, hidden 7168, 256
+experts, top-8, intermediate 2048; softmax top-k routing; e4m3 activations with 1x128 scales)
+over synthetic inputs; with N > 1 (launched by torch.distributed.run) the layer is
+expert-parallel: 4096/N tokens and 256/N experts per rank, all-to-all dispatch and combine over
+NCCL, and ``value`` is the whole job's TFLOP/s (total work fixed: strong scaling).
+
+``value``  : inputs resident in HBM before the timed region (CUDA events, barrier + synchronize on
+             both sides, max over ranks).
+``e2e``    : the same metric through the public Python API with HOST buffers: every step copies
+             the step's activations and router logits from pinned memory to the device and reads
+             the bf16 output back; expert weights are model state and stay resident.
+``roofline``: the dominant kernel (grouped GEMM1 + SwiGLU), algorithmic bytes / CUDA-event time
+             against the measured HBM copy bandwidth.
+``cpu_baseline`` / ``--impl reference``: the reference's CPU oracle arithmetic for the same layer
+             (oracle/moe.py, a restatement pinned bit-for-bit to the reference's oracle), timed on
+             the host cores over a bounded sample of the workload.
+The four per-GPU operators (RMSNorm, block-scaled GEMM, paged GQA / MLA decode) are timed at N = 1
+and reported under ``operators``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPE = dict(tokens=4096, hidden=7168, inter=2048, experts=256, top_k=8)
+WORKLOAD = "fp8_moe_dsv3_T4096_H7168_E256_top8_I2048_softmax_routing_e4m3_act"
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        doc = json.loads(path.read_text())
+        return {"hbm_gbs": float(doc["hbm_gbs"]), "bf16_tflops": float(doc["bf16_tflops"]),
+                "bf16_tflops_sustained": float(doc.get("bf16_tflops_sustained", doc["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        self.file.flush()
+        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 8]
+        os.unlink(self.file.name)
+        sm = []
+        reasons = set()
+        max_mhz = None
+        for r in rows:
+            try:
+                sm.append(float(r[1])); max_mhz = float(r[2])
+            except ValueError:
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if cell.strip().lower().startswith("active"):
+                    reasons.add(name)
+        busy = [v for v in sm if max_mhz and v > 0.5 * max_mhz] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max_mhz, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    elif n_gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(step, steps: int, warmup: int, world: int) -> float:
+    """Milliseconds per step: W untimed steps, then exactly K steps between two events bracketed by
+    barrier + synchronize; max over ranks."""
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    barrier(world)
+    return max_over_ranks(start.elapsed_time(stop) / steps, world)
+
+
+_flush = None
+
+
+def flush_l2():
+    """Evicts L2 (126 MB) by overwriting a 512 MB buffer."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_cold(launch, iters: int, warmup: int) -> float:
+    """Mean milliseconds of `launch` alone with L2 flushed before every timed launch."""
+    for _ in range(warmup):
+        launch()
+    times = []
+    for _ in range(iters):
+        flush_l2()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(); launch(); stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    return statistics.mean(times)
+
+
+# ------------------------------------------------------------------------------------------------
+def moe_single(steps, warmup, peaks):
+    import open_cake_ir_b200 as cake
+    dev = cake.workloads.moe_inputs(tokens=SHAPE["tokens"], hidden=SHAPE["hidden"], inter=SHAPE["inter"],
+                                    experts=SHAPE["experts"], local_experts=SHAPE["experts"], local_offset=0,
+                                    routing="softmax", device="cuda", gen_device="cuda")
+    out = torch.empty((SHAPE["tokens"], SHAPE["hidden"]), dtype=torch.bfloat16, device="cuda")
+    op = cake.Fp8Moe(dev, out, routing="softmax", act_mode="fp8")
+    flops = cake.workloads.moe_flops(SHAPE["tokens"], SHAPE["hidden"], SHAPE["inter"])
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        ms = time_steps(op.launch, steps, warmup, 1)
+    if op.status():
+        raise RuntimeError("a device-side wait ran out")
+    # stage timing (inputs 11 GB >> L2, so consecutive launches are cold anyway)
+    stage_ms = [0.0] * 4
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps)]
+    for k in range(steps):
+        events[k][0].record()
+        for s in range(4):
+            op.launch_stage(s)
+            events[k][s + 1].record()
+    torch.cuda.synchronize()
+    for k in range(steps):
+        for s in range(4):
+            stage_ms[s] += events[k][s].elapsed_time(events[k][s + 1]) / steps
+    pairs = SHAPE["tokens"] * SHAPE["top_k"]
+    gemm1_bytes = SHAPE["experts"] * 2 * SHAPE["inter"] * SHAPE["hidden"] + pairs * (SHAPE["hidden"] + SHAPE["inter"])
+    achieved = gemm1_bytes / (stage_ms[1] * 1e-3) / 1e9
+    roofline = {"kernel": "gemm_fp8_kernel<kGateUp> (grouped GEMM1 + SwiGLU + e4m3 requantisation)", "bound": "hbm",
+                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "peak_source": peaks["source"], "algorithmic_bytes": gemm1_bytes, "ms": stage_ms[1], "traffic": None,
+                "tflops": 2 * pairs * 2 * SHAPE["inter"] * SHAPE["hidden"] / (stage_ms[1] * 1e-3) / 1e12}
+    # end to end with host buffers
+    host_in = {k: dev[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
+    host_out = torch.empty_like(out, device="cpu").pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = out.numel() * out.element_size()
+
+    def e2e_step():
+        for k, t in host_in.items():
+            dev[k].copy_(t, non_blocking=True)
+        op.launch()
+        host_out.copy_(out, non_blocking=True)
+
+    e2e_ms = time_steps(e2e_step, steps, warmup, 1)
+    return {"ms": ms, "flops": flops, "clocks": clocks.summary(), "stage_ms": dict(zip(cake.Fp8Moe.STAGES, stage_ms)),
+            "roofline": roofline, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h, "launches": 8 * steps}
+
+
+def moe_parallel(steps, warmup, world, rank):
+    import open_cake_ir_b200 as cake
+    from open_cake_ir_b200 import ep
+    t_local, e_local = SHAPE["tokens"] // world, SHAPE["experts"] // world
+    dev = cake.workloads.moe_inputs(tokens=t_local, hidden=SHAPE["hidden"], inter=SHAPE["inter"], experts=SHAPE["experts"],
+                                    local_experts=e_local, local_offset=rank * e_local, routing="softmax", device="cuda",
+                                    gen_device="cuda", first_token=rank * t_local, total_tokens=SHAPE["tokens"])
+    route_factory, local_layer = ep.native_layer(dev, capacity=SHAPE["tokens"], experts=SHAPE["experts"])
+    layer = ep.ExpertParallelMoe(experts=SHAPE["experts"], top_k=SHAPE["top_k"], hidden=SHAPE["hidden"],
+                                 capacity=SHAPE["tokens"], route=route_factory("softmax"), local_layer=local_layer)
+    args = [dev[k] for k in ("routing_logits", "routing_bias", "routed_scaling_factor", "hidden_states", "hidden_states_scale")]
+    result = {}
+
+    def step():
+        result["out"] = layer.forward(*args)
+
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        ms = time_steps(step, steps, warmup, world)
+    host_in = {k: dev[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
+    host_out = torch.empty((t_local, SHAPE["hidden"]), dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = host_out.numel() * 2
+
+    def e2e_step():
+        for k, t in host_in.items():
+            dev[k].copy_(t, non_blocking=True)
+        step()
+        host_out.copy_(result["out"], non_blocking=True)
+
+    e2e_ms = time_steps(e2e_step, steps, warmup, world)
+    flops = cake.workloads.moe_flops(SHAPE["tokens"], SHAPE["hidden"], SHAPE["inter"])
+    return {"ms": ms, "flops": flops, "clocks": clocks.summary(), "e2e_ms": e2e_ms, "h2d": h2d * world, "d2h": d2h * world,
+            "launches": 9 * steps, "rows_sent_rank0": sum(layer.last_counts[0])}
+
+
+def per_gpu_operators(peaks, iters=20, warmup=3):
+    """RMSNorm, block-scaled GEMM, paged GQA and MLA decode at their serving shapes, L2 flushed before
+    every timed launch; algorithmic bytes or flops over the CUDA-event time."""
+    import open_cake_ir_b200 as cake
+    rows = []
+    inputs, meta = cake.workloads.rmsnorm_inputs(4096, 4096, device="cuda", gen_device="cuda")
+    out = torch.empty_like(inputs["x"])
+    op = cake.RmsNorm(inputs["x"], inputs["weight"], out, meta["epsilon"])
+    ms = time_cold(op.launch, iters, warmup)
+    nbytes = 2 * 4096 * 4096 * 2 + 4096 * 2
+    rows.append({"operator": "rmsnorm", "workload": "x bf16 [4096,4096], eps 1e-6", "ms": ms, "bound": "hbm", "unit": "GB/s",
+                 "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"], "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"]})
+    del inputs, out, op
+
+    g = cake.workloads.block_scaled_gemm_inputs(8192, 4096, 7168, device="cuda", gen_device="cuda")
+    c = torch.empty((8192, 4096), dtype=torch.bfloat16, device="cuda")
+    op = cake.BlockScaledGemm(g["a"], g["sfa"], g["b"], g["sfb"], c)
+    ms = time_cold(op.launch, iters, warmup)
+    flops = 2 * 8192 * 4096 * 7168
+    fp8_peak = 2 * peaks["bf16_tflops"]
+    rows.append({"operator": "block_scaled_gemm", "workload": "M8192 N4096 K7168 e4m3, 1x128 / 128x128 fp32 scales", "ms": ms,
+                 "bound": "tensor", "unit": "TFLOP/s", "achieved": flops / ms / 1e9, "peak": fp8_peak,
+                 "peak_note": "2 x measured cuBLAS bf16 burst (fp8 dense is twice the bf16 rate)",
+                 "frac": flops / ms / 1e9 / fp8_peak, "frac_of_nominal_4500": flops / ms / 1e9 / 4500.0, "status": op.status()})
+    del g, c, op
+
+    dev, meta = cake.workloads.gqa_decode_inputs(device="cuda", gen_device="cuda")
+    out = torch.empty_like(dev["q"]); lse = torch.empty((64, 32), dtype=torch.float32, device="cuda")
+    op = cake.GqaPagedDecode(dev["q"], dev["k_cache"], dev["v_cache"], dev["kv_indptr"], dev["kv_indices"],
+                             dev["kv_last_page_len"], dev["sm_scale"], out, lse, max_kv_len=meta["max_kv_len"])
+    ms = time_cold(op.launch, iters, warmup)
+    total = int(meta["kv_lens"].sum())
+    nbytes = total * 2 * 8 * 128 * 2 + 2 * out.numel() * 2 + lse.numel() * 4 + dev["kv_indices"].numel() * 4
+    rows.append({"operator": "gqa_paged_decode", "workload": f"batch 64, 32/8 heads, d128, page 16, sum kv_len {total}",
+                 "ms": ms, "bound": "hbm", "unit": "GB/s", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"],
+                 "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"]})
+    del dev, out, lse, op
+
+    dev, meta = cake.workloads.mla_decode_inputs(device="cuda", gen_device="cuda")
+    out = torch.empty_like(dev["q_nope"]); lse = torch.empty((32, 128), dtype=torch.float32, device="cuda")
+    op = cake.MlaPagedDecode(dev["q_nope"], dev["q_pe"], dev["ckv_cache"], dev["kpe_cache"], dev["kv_indptr"],
+                             dev["kv_indices"], dev["kv_last_page_len"], dev["sm_scale"], out, lse, max_kv_len=meta["max_kv_len"])
+    ms = time_cold(op.launch, iters, warmup)
+    total = int(meta["kv_lens"].sum())
+    nbytes = total * 1152 + dev["q_nope"].numel() * 2 + dev["q_pe"].numel() * 2 + out.numel() * 2
+    flops = total * 128 * 2176
+    rows.append({"operator": "mla_paged_decode", "workload": f"batch 32, 128 heads, ckv 512 + kpe 64, page 64, sum kv_len {total}",
+                 "ms": ms, "bound": "hbm", "unit": "GB/s", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"],
+                 "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"], "tflops": flops / ms / 1e9,
+                 "tensor_frac_of_bf16_burst": flops / ms / 1e9 / peaks["bf16_tflops"]})
+    return rows
+
+
+# ------------------------------------------------------------------------------------------------
+CPU_SAMPLE = dict(tokens=256, local_experts=8, local_offset=0)
+
+
+def cpu_reference_step(state):
+    """One bounded sample of the workload on the host: 256 tokens routed over all 256 experts, the
+    contributions of the first 8 experts computed by the oracle in fp32 on all host threads."""
+    from oracle import moe as oracle_moe
+    t0 = time.perf_counter()
+    result = oracle_moe.moe_reference(state["inputs"], routing="softmax", act_quant="fp8", dtype=torch.float32, return_parts=True)
+    seconds = time.perf_counter() - t0
+    local = (result["expert_ids"] >= CPU_SAMPLE["local_offset"]) & (result["expert_ids"] < CPU_SAMPLE["local_offset"] + CPU_SAMPLE["local_experts"])
+    pairs = int(local.sum())
+    flops = 2 * pairs * (SHAPE["hidden"] * 2 * SHAPE["inter"] + SHAPE["inter"] * SHAPE["hidden"])
+    return flops, seconds
+
+
+def cpu_state():
+    import open_cake_ir_b200 as cake
+    torch.set_num_threads(os.cpu_count() or 1)
+    inputs = cake.workloads.moe_inputs(tokens=CPU_SAMPLE["tokens"], hidden=SHAPE["hidden"], inter=SHAPE["inter"],
+                                       experts=SHAPE["experts"], local_experts=CPU_SAMPLE["local_experts"],
+                                       local_offset=CPU_SAMPLE["local_offset"], routing="softmax", device="cpu")
+    return {"inputs": inputs}
+
+
+def cpu_baseline(steps=1, warmup=0):
+    state = cpu_state()
+    for _ in range(warmup):
+        cpu_reference_step(state)
+    flops = seconds = 0.0
+    for _ in range(steps):
+        f, s = cpu_reference_step(state)
+        flops += f; seconds += s
+    return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{CPU_SAMPLE['tokens']} tokens routed over 256 experts, contributions of {CPU_SAMPLE['local_experts']} experts, "
+                      f"fp32 oracle (oracle/moe.py), {steps} pass(es), {seconds:.1f} s",
+            "seconds": seconds}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_baseline(steps=max(1, args.steps), warmup=min(1, args.warmup))
+    ms = base["seconds"] / max(1, args.steps) * 1e3
+    line = {"impl": "reference", "metric": "fp8_moe_tflops", "value": base["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 host arithmetic over e4m3 inputs", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "reference CPU oracle arithmetic on a bounded sample of the workload"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="native", choices=["native", "reference"])
+    parser.add_argument("--skip-operators", action="store_true", help="time only the MoE layer")
+    parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the native path has no CPU fallback")
+    world, rank, _ = dist_setup(args.gpus)
+    peaks = measured_peaks()
+    warmup = max(3, args.warmup)
+    if world == 1:
+        r = moe_single(args.steps, warmup, peaks)
+    else:
+        r = moe_parallel(args.steps, warmup, world, rank)
+    line = {"metric": "fp8_moe_tflops", "value": r["flops"] / (r["ms"] * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"ep{world}", "tokens_per_rank": SHAPE["tokens"] // world,
+                       "experts_per_rank": SHAPE["experts"] // world,
+                       "l2": "inputs larger than L2 (expert weights 11.3 GB over all ranks)"},
+            "clocks": r["clocks"],
+            "e2e": {"value": r["flops"] / (r["e2e_ms"] * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": r["e2e_ms"],
+                    "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
+            "gpu_launches": r["launches"],
+            "pct_of_fp8_nominal_peak": r["flops"] / (r["ms"] * 1e-3) / 1e12 / (4500.0 * world)}
+    if world == 1:
+        line["roofline"] = r["roofline"]
+        line["stage_ms"] = r["stage_ms"]
+        weight_bytes = SHAPE["experts"] * 3 * SHAPE["inter"] * SHAPE["hidden"]
+        line["layer_hbm_floor_ms"] = weight_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3
+        if not args.skip_operators:
+            line["operators"] = per_gpu_operators(peaks)
+        if not args.skip_cpu:
+            base = cpu_baseline()
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    else:
+        line["rows_sent_rank0"] = r["rows_sent_rank0"]
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -75,7 +75,7 @@ int cake_b200_rmsnorm_destroy(void* handle);
  * oracle tools/kernel_oracles.py:98-112):
  *   c[m,n] = bf16( sum_k a[m,k]*sfa[k/128,m] * b[n,k]*sfb[n/128,k/128] ), fp32 accumulation
  * buffers: a e4m3 [M,K], sfa fp32 [K/128,M], b e4m3 [N,K], sfb fp32 [N/128,K/128], c bf16 [M,N],
- *          workspace (>= cake_b200_block_scaled_gemm_workspace_bytes).  K % 128 == 0, N % 256 == 0.
+ *          workspace (>= cake_b200_block_scaled_gemm_workspace_bytes).  K % 128 == 0, N % 128 == 0.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   int64_t m, n, k;
@@ -134,7 +134,7 @@ int cake_b200_moe_permute_destroy(void* handle);
  * act_mode: 0 = intermediate activation requantised to e4m3 per (row,128) with amax/448 scales (one FP8 term);
  *           1 = two FP8 terms (value + residual), which carries the intermediate at better than bf16
  *               precision and meets the reference contract's tolerance against its unquantised oracle.
- * H % 256 == 0, I % 128 == 0.
+ * H % 128 == 0, I % 128 == 0.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   int64_t tokens;
@@ -148,6 +148,9 @@ typedef struct {
 size_t cake_b200_moe_workspace_bytes(const cake_b200_moe_config* config);
 int cake_b200_moe_create(void** buffers, const cake_b200_moe_config* config, void** handle_out);
 int cake_b200_moe_launch(void* handle, void* cuda_stream);
+/* One part of the layer at a time, in order 0..3 (0 routing + permute + gather, 1 grouped GEMM1 + SwiGLU,
+ * 2 grouped GEMM2, 3 combine), so that a caller can put events between the parts; launch == stages 0,1,2,3. */
+int cake_b200_moe_launch_stage(void* handle, int stage, void* cuda_stream);
 int cake_b200_moe_destroy(void* handle);
 /* Device pointers of intermediates inside the workspace, for tests and for expert-parallel callers:
  * which = 0 expert_ids int32 [T,top_k]; 1 route_weights fp32 [T,top_k]; 2 counts; 3 offsets; 4 sorted_pairs; 5 inv_perm. */
@@ -173,8 +176,9 @@ int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream);
 int cake_b200_gqa_decode_destroy(void* handle);
 
 /* ------------------------------------------------------------------------------------------
- * Paged MLA decode (absorbed form).  Same launch plan and oracle as above, MLA branch
- * (attention.py:164-165, :175-177; spec attention_specs.py:249-292):
+ * Paged MLA decode (absorbed form).  Replaces the same four-stage launch plan
+ * (src/open_cake_ir/tasks/solx_fib/attention.py:190-331) for the MLA branch of the oracle
+ * (attention.py:164-165, :175-177; spec src/open_cake_ir/tasks/solx_fib/attention_specs.py:249-292):
  *   logits = (ckv . q_nope + kpe . q_pe) * sm_scale; out = bf16(softmax(logits) ckv); lse base 2.
  * buffers: q_nope bf16 [B,H,512], q_pe bf16 [B,H,64], ckv_cache bf16 [pages,page_size,512],
  *          kpe_cache bf16 [pages,page_size,64], kv_indptr int32 [B+1], kv_indices int32 [*],

@@ -295,6 +295,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Splits two fp32 values into a bf16 pair plus the bf16 pair of what the first rounding lost, so
+// that hi + lo carries about 16 significant bits through a bf16 tensor-core operand.
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
+  __nv_bfloat162 h; h.x = ah; h.y = bh;
+  __nv_bfloat162 l = __floats2bfloat162_rn(a - __bfloat162float(ah), b - __bfloat162float(bh));
+  hi = *reinterpret_cast<uint32_t*>(&h);
+  lo = *reinterpret_cast<uint32_t*>(&l);
+}
 // Four floats -> four e4m3 bytes (round to nearest even, saturating to +-448).
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
   __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);

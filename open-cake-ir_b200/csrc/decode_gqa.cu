@@ -10,7 +10,8 @@
 // row per token and head, XOR-swizzled in shared memory), so there is no CTA-wide barrier in
 // the main loop.  The G = Hq/Hkv query heads that share a KV head are the rows of an
 // m16n8k16 bf16 MMA (rows beyond G are zero): S = Q K^T via ldmatrix on the K tile, online
-// softmax in base 2 with warp shuffles, O += P V via ldmatrix.trans on the V tile.  Warps are
+// softmax in base 2 with warp shuffles, O += P V via ldmatrix.trans on the V tile (P as two bf16
+// terms, so the weights keep ~16 significant bits).  Warps are
 // merged in shared memory, chunks by a second small kernel.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
@@ -172,8 +173,12 @@ gqa_decode_kernel(const Params p) {
     psum += __shfl_xor_sync(0xffffffffu, psum, 2);
     l = l * alpha + psum;
     m = m_new;
-    const uint32_t pa0 = pack_bf16x2(pr[0], pr[1]);   // tokens 0..7 of the tile  (A cols k..k+1)
-    const uint32_t pa2 = pack_bf16x2(pr[2], pr[3]);   // tokens 8..15             (A cols k+8..)
+    // P enters the tensor core as two bf16 terms (value + rounding residual): a single bf16 term
+    // would put 2^-9 relative error on every weight, more than the contract's tolerance allows
+    // once the weighted values cancel.
+    uint32_t pa0, pa2, pb0, pb2;
+    split_bf16x2(pr[0], pr[1], pa0, pb0);             // tokens 0..7 of the tile  (A cols k..k+1)
+    split_bf16x2(pr[2], pr[3], pa2, pb2);             // tokens 8..15             (A cols k+8..)
 #pragma unroll
     for (int n = 0; n < 16; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
     // O += P V : V^T fragments through ldmatrix.trans, 16 dims per instruction
@@ -184,7 +189,9 @@ gqa_decode_kernel(const Params p) {
       const int trow = (mi & 1) * 8 + (lane & 7);       // matrices 0/1: tokens 0-7 / 8-15; 2/3: next 8 dims
       ldmatrix_x4_trans(v_smem + tile_off(trow, np * 2 + (mi >> 1)), b0, b1, b2, b3);
       mma_bf16_16816(o[np * 2], pa0, 0u, pa2, 0u, b0, b1);
+      mma_bf16_16816(o[np * 2], pb0, 0u, pb2, 0u, b0, b1);
       mma_bf16_16816(o[np * 2 + 1], pa0, 0u, pa2, 0u, b2, b3);
+      mma_bf16_16816(o[np * 2 + 1], pb0, 0u, pb2, 0u, b2, b3);
     }
     __syncwarp();
     const int next = i + kRing - 1;

@@ -174,14 +174,14 @@ mla_decode_kernel(const Params p) {
     const float alpha0 = exp2f(m0 - n0), alpha1 = exp2f(m1 - n1);
     m0 = n0; m1 = n1;
     float sum0 = 0.f, sum1 = 0.f;
-    uint32_t pa[4][2];       // P as bf16 pairs: [n-tile][row | row+8]
+    uint32_t pa[4][2], pb[4][2];   // P as bf16 pairs, value and rounding residual: [n-tile][row | row+8]
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
       const float p0 = exp2f(s[n][0] - n0), p1 = exp2f(s[n][1] - n0);
       const float p2 = exp2f(s[n][2] - n1), p3 = exp2f(s[n][3] - n1);
       sum0 += p0 + p1; sum1 += p2 + p3;
-      pa[n][0] = pack_bf16x2(p0, p1);
-      pa[n][1] = pack_bf16x2(p2, p3);
+      split_bf16x2(p0, p1, pa[n][0], pb[n][0]);
+      split_bf16x2(p2, p3, pa[n][1], pb[n][1]);
     }
     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
     sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
@@ -197,7 +197,9 @@ mla_decode_kernel(const Params p) {
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4_trans(kv + row_off(ks * 16 + (mi & 1) * 8 + lr, dh * 32 + np * 2 + (mi >> 1)), b0, b1, b2, b3);
         mma_bf16_16816(o[np * 2], pa[ks * 2][0], pa[ks * 2][1], pa[ks * 2 + 1][0], pa[ks * 2 + 1][1], b0, b1);
+        mma_bf16_16816(o[np * 2], pb[ks * 2][0], pb[ks * 2][1], pb[ks * 2 + 1][0], pb[ks * 2 + 1][1], b0, b1);
         mma_bf16_16816(o[np * 2 + 1], pa[ks * 2][0], pa[ks * 2][1], pa[ks * 2 + 1][0], pa[ks * 2 + 1][1], b2, b3);
+        mma_bf16_16816(o[np * 2 + 1], pb[ks * 2][0], pb[ks * 2][1], pb[ks * 2 + 1][0], pb[ks * 2 + 1][1], b2, b3);
       }
     }
   }

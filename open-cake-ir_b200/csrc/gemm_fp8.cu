@@ -29,7 +29,7 @@ extern "C" int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b20
   for (int i = 0; i < 6; ++i)
     if (!buffers[i] || (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
   const int64_t m = config->m, n = config->n, k = config->k;
-  if (m <= 0 || n <= 0 || k <= 0 || (k % gemm::kBK) || (n % gemm::kBN) || m > INT32_MAX / 2 || n > INT32_MAX / 2)
+  if (m <= 0 || n <= 0 || k <= 0 || (k % gemm::kBK) || (n % 128) || m > INT32_MAX / 2 || n > INT32_MAX / 2)
     return kErrBadArgument;
   auto* h = new (std::nothrow) DenseHandle;
   if (!h) return int(cudaErrorMemoryAllocation);
@@ -53,7 +53,7 @@ extern "C" int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b20
   p.out = buffers[4];
   h->status = static_cast<int*>(buffers[5]);
   p.status = h->status;
-  const long long items = ((m + gemm::kBM - 1) / gemm::kBM) * (n / gemm::kBN);
+  const long long items = ((m + gemm::kBM - 1) / gemm::kBM) * ((n + gemm::kBN - 1) / gemm::kBN);
   const int sms = sm_count(device);
   h->grid = int(items < sms ? items : sms);
   *handle_out = h;

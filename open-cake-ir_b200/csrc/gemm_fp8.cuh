@@ -112,7 +112,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tiles = (MODE == kGateUp) ? p.n / 128 : p.n / kBN;
+  const int n_tiles = (MODE == kGateUp) ? p.n / 128 : (p.n + kBN - 1) / kBN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
@@ -233,7 +233,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         sfb_row0 = item.n_tile;
         sfb_row1 = p.n / 128 + item.n_tile;
       } else {
-        sfb_row0 = sfb_row1 = item.n_tile * 2 + half;
+        sfb_row0 = sfb_row1 = min(item.n_tile * 2 + half, sfb_rows - 1);
       }
       const float* sfb0 = p.sfb + (size_t(item.group) * sfb_rows + sfb_row0) * p.b_k_blocks;
       const float* sfb1 = p.sfb + (size_t(item.group) * sfb_rows + sfb_row1) * p.b_k_blocks;
@@ -274,7 +274,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       }
       if (!ok) break;
-      const bool valid = r < item.rows_valid;
+      // rows past the group's end and, where N is an odd multiple of 128, the tile's second column half hold nothing
+      const bool valid = r < item.rows_valid && (MODE == kGateUp || item.n_tile * kBN + half * 128 < p.n);
 
       if (MODE == kDense) {
         if (valid) {

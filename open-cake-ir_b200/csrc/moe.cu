@@ -435,7 +435,7 @@ extern "C" int cake_b200_moe_permute_destroy(void* handle) {
 // ------------------------------------------------------------------------------------------
 static bool moe_config_ok(const cake_b200_moe_config& c) {
   if (c.tokens < 0 || c.tokens * int64_t(c.top_k > 0 ? c.top_k : 1) > (int64_t(1) << 28)) return false;
-  if (c.hidden <= 0 || c.hidden % cake::gemm::kBN || c.intermediate <= 0 || c.intermediate % 128) return false;
+  if (c.hidden <= 0 || c.hidden % 128 || c.intermediate <= 0 || c.intermediate % 128) return false;
   if (c.local_experts <= 0 || c.local_experts > cake::gemm::kMaxGroups || c.local_experts > c.experts) return false;
   if (c.act_mode != 0 && c.act_mode != 1) return false;
   if (c.top_k <= 0 || c.top_k > 32) return false;
@@ -526,35 +526,60 @@ extern "C" int cake_b200_moe_create(void** buffers, const cake_b200_moe_config* 
   return 0;
 }
 
-extern "C" int cake_b200_moe_launch(void* handle, void* cuda_stream) {
+// stage 0: routing + permute + gather; 1: grouped GEMM1 + SwiGLU; 2: grouped GEMM2; 3: combine
+static int moe_launch_stage(cake::moe::MoeHandle* h, int stage, cudaStream_t s) {
+  using namespace cake;
+  const cake_b200_moe_config& c = h->cfg;
+  const moe::Layout& l = h->layout;
+  const int tokens = int(c.tokens);
+  moe::PermuteArgs pa{h->expert_ids, h->local_offset, reinterpret_cast<int*>(h->ws + l.counts),
+                      reinterpret_cast<int*>(h->ws + l.offsets), reinterpret_cast<int*>(h->ws + l.sorted_pairs),
+                      reinterpret_cast<int*>(h->ws + l.inv_perm), tokens * c.top_k, c.local_experts};
+  switch (stage) {
+    case 0: {
+      CAKE_CUDA_OK(cudaMemsetAsync(h->ws + l.status, 0, 256, s));
+      if (!c.external_routing)
+        moe::launch_routing(h->logits, h->bias, h->factor, h->expert_ids, h->route_weights, tokens, c.experts, c.top_k,
+                            c.n_group, c.topk_group, c.routing_mode, s);
+      if (int rc = moe::launch_permute(pa, s)) return rc;
+      const int gather_blocks = (l.capacity + 7) / 8;
+      moe::gather_kernel<<<gather_blocks < 4096 ? gather_blocks : 4096, 256, 0, s>>>(
+          h->hidden, h->hidden_scale, h->route_weights, pa.sorted_pairs, pa.offsets, h->ws + l.x_perm,
+          reinterpret_cast<float*>(h->ws + l.sx_perm), reinterpret_cast<float*>(h->ws + l.row_weight), tokens, c.hidden,
+          c.top_k, c.local_experts, l.capacity);
+      break;
+    }
+    case 1:
+      gemm::gemm_fp8_kernel<gemm::kGateUp><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a1, h->map_b1, h->p1);
+      break;
+    case 2:
+      gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_b2, h->p2);
+      break;
+    case 3:
+      moe::combine_kernel<<<tokens, 256, 0, s>>>(reinterpret_cast<const float*>(h->ws + l.y), pa.inv_perm, h->output,
+                                                 c.hidden, c.top_k);
+      break;
+    default:
+      return kErrBadArgument;
+  }
+  return int(cudaGetLastError());
+}
+
+extern "C" int cake_b200_moe_launch_stage(void* handle, int stage, void* cuda_stream) {
   using namespace cake;
   if (!handle) return kErrBadArgument;
   auto* h = static_cast<moe::MoeHandle*>(handle);
   int device = -1;
   CAKE_CUDA_OK(cudaGetDevice(&device));
   if (device != h->device) return kErrWrongDevice;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
-  const cake_b200_moe_config& c = h->cfg;
-  const moe::Layout& l = h->layout;
-  CAKE_CUDA_OK(cudaMemsetAsync(h->ws + l.status, 0, 256, s));
-  const int tokens = int(c.tokens);
-  if (tokens == 0) return 0;
-  if (!c.external_routing)
-    moe::launch_routing(h->logits, h->bias, h->factor, h->expert_ids, h->route_weights, tokens, c.experts, c.top_k, c.n_group,
-                        c.topk_group, c.routing_mode, s);
-  moe::PermuteArgs pa{h->expert_ids, h->local_offset, reinterpret_cast<int*>(h->ws + l.counts),
-                      reinterpret_cast<int*>(h->ws + l.offsets), reinterpret_cast<int*>(h->ws + l.sorted_pairs),
-                      reinterpret_cast<int*>(h->ws + l.inv_perm), tokens * c.top_k, c.local_experts};
-  if (int rc = moe::launch_permute(pa, s)) return rc;
-  const int gather_blocks = (l.capacity + 7) / 8;
-  moe::gather_kernel<<<gather_blocks < 4096 ? gather_blocks : 4096, 256, 0, s>>>(
-      h->hidden, h->hidden_scale, h->route_weights, pa.sorted_pairs, pa.offsets, h->ws + l.x_perm,
-      reinterpret_cast<float*>(h->ws + l.sx_perm), reinterpret_cast<float*>(h->ws + l.row_weight), tokens, c.hidden, c.top_k,
-      c.local_experts, l.capacity);
-  gemm::gemm_fp8_kernel<gemm::kGateUp><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a1, h->map_b1, h->p1);
-  gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_b2, h->p2);
-  moe::combine_kernel<<<tokens, 256, 0, s>>>(reinterpret_cast<const float*>(h->ws + l.y), pa.inv_perm, h->output, c.hidden, c.top_k);
-  return int(cudaGetLastError());
+  if (h->cfg.tokens == 0) return stage >= 0 && stage <= 3 ? 0 : kErrBadArgument;
+  return moe_launch_stage(h, stage, reinterpret_cast<cudaStream_t>(cuda_stream));
+}
+
+extern "C" int cake_b200_moe_launch(void* handle, void* cuda_stream) {
+  for (int stage = 0; stage < 4; ++stage)
+    if (int rc = cake_b200_moe_launch_stage(handle, stage, cuda_stream)) return rc;
+  return 0;
 }
 
 extern "C" int cake_b200_moe_destroy(void* handle) {

@@ -120,8 +120,10 @@ extern "C" int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_
   int device = 0;
   if (int rc = require_blackwell(&device)) return rc;
   const int count = config->fused_residual ? 4 : 3;
-  for (int i = 0; i < count; ++i)
-    if (!buffers[i] || (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
+  for (int i = 0; i < count; ++i) {
+    const bool may_be_empty = config->rows == 0 && i != count - 2;      // only the weight row exists then
+    if ((!buffers[i] && !may_be_empty) || (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
+  }
   if (config->rows < 0 || config->rows > INT32_MAX || config->width <= 0 || (config->width & 7) ||
       config->width > 8 * 8 * kThreads || !(config->epsilon >= 0.f))
     return kErrBadArgument;

@@ -1,0 +1,153 @@
+"""Expert-parallel FP8 MoE layer: tokens sharded T/R per rank, experts sharded E/R per rank
+(rank r owns experts [r*E/R, (r+1)*E/R), the reference's ``local_expert_offset`` view,
+src/open_cake_ir/tasks/solx_fib/moe.py:139-146), joined by an all-to-all dispatch and an
+all-to-all combine over ``torch.distributed`` (NCCL over NVLink on the GPU box; gloo in the CPU
+tests of the exchange logic).
+
+Per layer and rank:
+  1. route the rank's own tokens (native routing kernel);
+  2. for every destination rank that owns at least one of a token's experts, send the token ONCE:
+     its e4m3 row, its K-block scales, its expert ids and route weights, packed into one byte row;
+     one small all-to-all carries the per-rank row counts, one all-to-all the rows;
+  3. run the rank-local layer on the received rows with routing given from outside -- pairs whose
+     expert the rank does not own contribute nothing (moe.py:145-146) -- which yields, per received
+     row, the bf16 sum of its local experts' weighted contributions;
+  4. return those partial rows by the reverse all-to-all; the owner adds the at most R partial rows
+     of a token in rank order in fp32 and rounds once to bf16.
+
+The exchange plan is plain index arithmetic on the rank's device; ``route`` and ``local_layer`` are
+injected so that the same class runs the native kernels on a GPU and the CPU oracle under gloo.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def exchange_plan(expert_ids: torch.Tensor, world: int, experts: int):
+    """expert_ids int [T, K] -> (send_tokens [n] ordered by destination rank then token,
+    send_counts [world], slot_of [T, world] = position of token t in the send list for rank r or -1)."""
+    per_rank = experts // world
+    dest = torch.div(expert_ids.long(), per_rank, rounding_mode="floor")
+    ranks = torch.arange(world, device=expert_ids.device)
+    needs = (dest[:, :, None] == ranks[None, None, :]).any(dim=1)          # [T, world]
+    order = torch.nonzero(needs.t())                                      # rows (rank, token), rank-major
+    send_tokens = order[:, 1]
+    send_counts = needs.sum(dim=0)
+    slot_of = torch.full(needs.shape, -1, dtype=torch.long, device=expert_ids.device)
+    slot_of[order[:, 1], order[:, 0]] = torch.arange(order.shape[0], device=expert_ids.device)
+    return send_tokens, send_counts, slot_of
+
+
+def pack_rows(hidden_u8, hidden_scale, expert_ids, route_weights, tokens):
+    """One byte row per sent token: H e4m3 bytes | H/128 fp32 scales | K int32 ids | K fp32 weights."""
+    rows = hidden_u8[tokens]
+    scales = hidden_scale.t()[tokens].contiguous().view(torch.uint8)
+    ids = expert_ids[tokens].contiguous().view(torch.uint8)
+    weights = route_weights[tokens].contiguous().view(torch.uint8)
+    return torch.cat([rows, scales, ids, weights], dim=1).contiguous()
+
+
+def row_bytes(hidden: int, top_k: int) -> int:
+    return hidden + 4 * (hidden // 128) + 8 * top_k
+
+
+class ExpertParallelMoe:
+    """``forward()`` runs one layer over this rank's tokens.
+
+    ``route(logits, bias, factor) -> (ids int32 [T,K], weights fp32 [T,K])`` and
+    ``local_layer(hidden e4m3 [cap,H], scale fp32 [H/128,cap], ids int32 [cap,K], weights fp32 [cap,K])
+    -> bf16 [cap,H]`` are the rank's routing and rank-local expert layer; ``capacity`` is the largest
+    number of rows a rank can receive (the global token count)."""
+
+    def __init__(self, *, experts: int, top_k: int, hidden: int, capacity: int, route, local_layer, group=None,
+                 device="cuda"):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.experts, self.top_k, self.hidden, self.capacity = experts, top_k, hidden, capacity
+        self.route, self.local_layer = route, local_layer
+        self.device = torch.device(device)
+        kb = hidden // 128
+        self.recv_hidden = torch.zeros((capacity, hidden), dtype=torch.uint8, device=self.device)
+        self.recv_scale = torch.zeros((kb, capacity), dtype=torch.float32, device=self.device)
+        self.recv_ids = torch.full((capacity, top_k), -1, dtype=torch.int32, device=self.device)
+        self.recv_weights = torch.zeros((capacity, top_k), dtype=torch.float32, device=self.device)
+        self.last_counts = None
+
+    def _all_to_all(self, out, inp, out_split, in_split):
+        if self.world == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out, inp, out_split, in_split, group=self.group)
+
+    def forward(self, routing_logits, routing_bias, routed_scaling_factor, hidden_states, hidden_states_scale):
+        tokens = hidden_states.shape[0]
+        kb = self.hidden // 128
+        ids, weights = self.route(routing_logits, routing_bias, routed_scaling_factor)
+        send_tokens, send_counts, slot_of = exchange_plan(ids, self.world, self.experts)
+        recv_counts = torch.empty_like(send_counts)
+        self._all_to_all(recv_counts, send_counts, None, None)
+        counts = torch.stack([send_counts, recv_counts]).cpu()             # the one host sync of the layer
+        send_split, recv_split = counts[0].tolist(), counts[1].tolist()
+        n_send, n_recv = sum(send_split), sum(recv_split)
+        if n_recv > self.capacity:
+            raise RuntimeError("received more rows than the layer was sized for")
+        self.last_counts = (send_split, recv_split)
+        packed = pack_rows(hidden_states.view(torch.uint8), hidden_states_scale, ids, weights, send_tokens)
+        width = row_bytes(self.hidden, self.top_k)
+        received = torch.empty((n_recv, width), dtype=torch.uint8, device=self.device)
+        self._all_to_all(received, packed, recv_split, send_split)
+        # unpack into the rank-local layer's fixed-capacity inputs; unused rows keep expert id -1
+        self.recv_ids.fill_(-1)
+        self.recv_hidden[:n_recv] = received[:, :self.hidden]
+        o = self.hidden
+        self.recv_scale[:, :n_recv] = received[:, o:o + 4 * kb].contiguous().view(torch.float32).t()
+        o += 4 * kb
+        self.recv_ids[:n_recv] = received[:, o:o + 4 * self.top_k].contiguous().view(torch.int32)
+        o += 4 * self.top_k
+        self.recv_weights[:n_recv] = received[:, o:o + 4 * self.top_k].contiguous().view(torch.float32)
+        partial = self.local_layer(self.recv_hidden.view(torch.float8_e4m3fn), self.recv_scale, self.recv_ids,
+                                   self.recv_weights)
+        returned = torch.empty((n_send + 1, self.hidden), dtype=torch.bfloat16, device=self.device)
+        returned[n_send].zero_()                                           # row -1 of the gather below
+        self._all_to_all(returned[:n_send], partial[:n_recv].contiguous(), send_split, recv_split)
+        out = torch.zeros((tokens, self.hidden), dtype=torch.float32, device=self.device)
+        for r in range(self.world):                                        # fixed rank order: deterministic sum
+            out += returned[slot_of[:, r]].float()
+        return out.to(torch.bfloat16)
+
+
+def native_layer(weights: dict, *, capacity: int, experts: int, top_k: int = 8, act_mode: str = "fp8", device="cuda"):
+    """(route, local_layer) built on the native kernels for one rank; ``weights`` holds the rank's
+    gemm1/gemm2 weights and scales and ``local_expert_offset``."""
+    from . import ops
+
+    state = {}
+
+    def route_factory(mode: str, n_group=8, topk_group=4):
+        def route(logits, bias, factor):
+            key = ("route", logits.data_ptr(), bias.data_ptr(), factor.data_ptr())
+            if key not in state:
+                t = logits.shape[0]
+                ids = torch.empty((t, top_k), dtype=torch.int32, device=device)
+                w = torch.empty((t, top_k), dtype=torch.float32, device=device)
+                state[key] = (ops.MoeRouting(logits, bias, factor, ids, w, top_k=top_k, n_group=n_group,
+                                             topk_group=topk_group, mode=mode), ids, w)
+            op, ids, w = state[key]
+            op.launch()
+            return ids, w
+        return route
+
+    def local_layer(hidden, scale, ids, w):
+        key = ("layer", hidden.data_ptr(), scale.data_ptr(), ids.data_ptr(), w.data_ptr())
+        if key not in state:
+            out = torch.empty((capacity, hidden.shape[1]), dtype=torch.bfloat16, device=device)
+            inputs = dict(weights)
+            inputs.update(expert_ids=ids, route_weights=w, hidden_states=hidden, hidden_states_scale=scale)
+            state[key] = (ops.Fp8Moe(inputs, out, experts=experts, top_k=top_k, act_mode=act_mode, external_routing=True), out)
+        op, out = state[key]
+        op.launch()
+        return out
+
+    return route_factory, local_layer

@@ -197,6 +197,15 @@ class Fp8Moe(_Operator):
         self._create(first + rest + [output], cfg, _lib.workspace_bytes(self.stem, cfg))
         self.tokens, self.top_k, self.local_experts = tokens, top_k, local_experts
 
+    STAGES = ("route_permute_gather", "gemm1_swiglu", "gemm2", "combine")
+
+    def launch_stage(self, stage: int, stream=None) -> None:
+        """One part of the layer (see STAGES); the four in order are exactly ``launch``."""
+        with torch.cuda.device(self.device):
+            code = _lib.library().cake_b200_moe_launch_stage(self.native.handle, stage, _stream(stream))
+        if code:
+            raise _lib.CakeError("cake_b200_moe_launch_stage", code)
+
     def intermediate(self, name: str) -> torch.Tensor:
         """Device view of an intermediate in the workspace (expert_ids, route_weights, counts,
         offsets, sorted_pairs, inv_perm) -- valid after a launch has completed."""

@@ -55,7 +55,9 @@ def route(inputs, routing: str, top_k: int = 8):
     if routing == "softmax":
         ids, w = routing_softmax_topk(inputs["routing_logits"], top_k)
         return ids, w * factor
-    raise ValueError("routing must be 'ds' or 'softmax'")
+    if routing == "external":     # routing decided elsewhere (expert-parallel receive side); ids outside the local interval are ignored
+        return inputs["expert_ids"].long(), inputs["route_weights"].float()
+    raise ValueError("routing must be 'ds', 'softmax' or 'external'")
 
 
 def moe_reference(inputs: dict, *, routing: str = "ds", act_quant: str = "none",

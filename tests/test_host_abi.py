@@ -1,0 +1,78 @@
+"""CPU tests of the drop-in boundary: the library loads without a GPU, exports every symbol the
+header declares, rejects null arguments before touching the device, and the target document's
+tensor ABI agrees with the reference's contract for the same operator."""
+import ctypes
+import json
+import re
+from pathlib import Path
+
+import pytest
+
+import open_cake_ir_b200 as cake
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "cake_b200.h").read_text()
+
+
+def declared_symbols():
+    return sorted(set(re.findall(r"\b(cake_b200_[a-z0-9_]+)\s*\(", HEADER)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = cake._lib.library()
+    names = declared_symbols()
+    assert len(names) >= 28
+    for name in names:
+        assert hasattr(lib, name), name
+    assert sorted(cake._lib.EXPORTS) == names
+    assert lib.cake_b200_abi_version() == 1
+
+
+def test_every_entry_point_cites_the_reference_interface_it_replaces():
+    for block in re.split(r"/\* -{20,}", HEADER)[1:]:
+        assert re.search(r"\b(src/open_cake_ir|corpus|tools)/[\w/.-]+(:\d+)?", block), block[:80]
+
+
+@pytest.mark.parametrize("stem", list(cake._lib.OPERATORS))
+def test_null_arguments_are_rejected_without_a_device(stem):
+    lib = cake._lib.library()
+    config, _ = cake._lib.OPERATORS[stem]
+    handle = ctypes.c_void_p()
+    assert getattr(lib, f"cake_b200_{stem}_create")(None, ctypes.byref(config()), ctypes.byref(handle)) == 20001
+    assert getattr(lib, f"cake_b200_{stem}_launch")(None, None) == 20001
+    assert getattr(lib, f"cake_b200_{stem}_destroy")(None) == 0
+
+
+def test_workspace_queries_are_pure_host_functions():
+    cfg = cake._lib.MoeConfig(4096, 7168, 2048, 256, 256, 8, 8, 4, 1, 0, 0)
+    size = cake._lib.workspace_bytes("moe", cfg)
+    pairs = 4096 * 8
+    assert size >= pairs * (7168 + 2048 + 7168 * 4) and size < 2 * pairs * (7168 + 2048 + 7168 * 4)
+    assert cake._lib.workspace_bytes("moe", cake._lib.MoeConfig(4096, 7168 + 1, 2048, 256, 256, 8, 8, 4, 1, 0, 0)) == 0
+    g = cake._lib.GqaDecodeConfig(64, 32, 8, 128, 16, 4096)
+    assert cake._lib.workspace_bytes("gqa_decode", g) > 64 * 32 * 129 * 4
+    assert cake._lib.workspace_bytes("gqa_decode", cake._lib.GqaDecodeConfig(64, 32, 5, 128, 16, 4096)) == 0
+
+
+def test_operators_refuse_cpu_tensors():
+    import torch
+    x = torch.zeros((4, 16), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        cake.rmsnorm(x, torch.ones(16, dtype=torch.bfloat16), 1e-6)
+
+
+def test_target_document_matches_the_contract_abi():
+    doc = cake.operators.target()
+    assert doc["nvcc_flags"] == ["--gpu-architecture=compute_100a", "--gpu-code=sm_100a"]
+    moe = [t["name"] for t in cake.operators.tensor_abi("fp8_moe")]
+    # src/open_cake_ir/tasks/solx_fib/moe.py:13-20, inputs then the output
+    assert moe == ["routing_logits", "routing_bias", "hidden_states", "hidden_states_scale", "gemm1_weights",
+                   "gemm1_weights_scale", "gemm2_weights", "gemm2_weights_scale", "local_expert_offset",
+                   "routed_scaling_factor", "output"]
+    gqa = [t["name"] for t in cake.operators.tensor_abi("gqa_paged_decode")]
+    assert gqa == ["q", "k_cache", "v_cache", "kv_indptr", "kv_indices", "kv_last_page_len", "sm_scale", "output", "lse"]
+    for name, op in doc["operators"].items():
+        for verb in ("create", "launch", "destroy"):
+            assert op["host_abi"][verb] in HEADER, (name, verb)
+        assert all(t["mode"] in ("input", "output") for t in op["tensors"])
+    assert json.dumps(doc)      # canonical JSON
