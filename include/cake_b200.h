@@ -176,6 +176,26 @@ int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream);
 int cake_b200_gqa_decode_destroy(void* handle);
 
 /* ------------------------------------------------------------------------------------------
+ * Paged GQA decode for callers that cannot allocate.  This entry point has no counterpart in the reference.
+ * It computes exactly what cake_b200_gqa_decode_* computes, from the same tensors, but takes no workspace and
+ * makes no handle: one call validates, launches on `cuda_stream` and returns.  It is meant for hosts that may
+ * not touch the CUDA allocator and have no scratch buffer to lend -- a server whose own pool already owns all of
+ * device memory, a plug-in sandbox that bans allocator calls, a loop that cannot take the synchronisation an
+ * allocation can imply.  The split-KV partial results go to a fixed 16 MiB array inside the library image
+ * (cake_b200_gqa_decode_noalloc_scratch_limit() returns the size); every GPU that loads the library holds that
+ * array until the process exits.  The call uses no cudaMalloc / cudaFree and no allocating library routine.
+ *   - Limit: batch * (max_kv_len / chunk + 1) * num_qo_heads * 129 * 4 bytes must fit in the array; the call
+ *     lengthens its KV chunks to make it fit and returns CAKE_B200_ERR_WORKSPACE (20004) when it still cannot.
+ *   - The first call on each device looks up the array's device address and sets the kernel's shared-memory
+ *     attribute (with that device current); make that first call before starting any stream capture.
+ *   - All calls share the array.  Nothing in it has to be cleared: a call reads back only what it wrote.
+ *     Calls that overlap on the GPU race on it; run them one after another.
+ * buffers: q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse (as above, no workspace).
+ * ---------------------------------------------------------------------------------------- */
+int cake_b200_gqa_decode_noalloc(void** buffers, const cake_b200_gqa_decode_config* config, void* cuda_stream);
+size_t cake_b200_gqa_decode_noalloc_scratch_limit(void);
+
+/* ------------------------------------------------------------------------------------------
  * Paged MLA decode (absorbed form).  Replaces the same four-stage launch plan
  * (src/open_cake_ir/tasks/solx_fib/attention.py:190-331) for the MLA branch of the oracle
  * (attention.py:164-165, :175-177; spec src/open_cake_ir/tasks/solx_fib/attention_specs.py:249-292):

@@ -70,7 +70,8 @@ OPERATORS = {
     "mla_decode": (MlaDecodeConfig, True),
 }
 # every symbol include/cake_b200.h declares
-EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage"]
+EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
+            "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit"]
            + [f"cake_b200_{stem}_{verb}" for stem in OPERATORS for verb in ("create", "launch", "destroy")]
            + [f"cake_b200_{stem}_workspace_bytes" for stem, (_, ws) in OPERATORS.items() if ws])
 
@@ -89,6 +90,9 @@ def library() -> ctypes.CDLL:
         lib.cake_b200_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
         lib.cake_b200_moe_intermediate.argtypes = [c_void_p, c_int, POINTER(c_void_p)]
         lib.cake_b200_moe_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
+        lib.cake_b200_gqa_decode_noalloc.argtypes = [POINTER(c_void_p), POINTER(GqaDecodeConfig), c_void_p]
+        lib.cake_b200_gqa_decode_noalloc.restype = c_int
+        lib.cake_b200_gqa_decode_noalloc_scratch_limit.restype = c_size_t
         for stem, (config, has_ws) in OPERATORS.items():
             create = getattr(lib, f"cake_b200_{stem}_create")
             create.argtypes = [POINTER(c_void_p), POINTER(config), POINTER(c_void_p)]

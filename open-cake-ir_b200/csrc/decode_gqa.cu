@@ -15,6 +15,7 @@
 // merged in shared memory, chunks by a second small kernel.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
+#include <mutex>
 #include <new>
 
 namespace cake {
@@ -350,4 +351,100 @@ extern "C" int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream) {
 extern "C" int cake_b200_gqa_decode_destroy(void* handle) {
   delete static_cast<cake::gqa::Handle*>(handle);
   return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Paged GQA decode without any allocation.
+//
+// Some hosts of this library may not call the CUDA allocator at all: a serving process whose own
+// pool already owns the whole of device memory (a cudaMalloc there fails or fragments the pool),
+// a plug-in sandbox that forbids allocator calls from plug-in code, or a latency-critical loop that
+// cannot afford the device-wide synchronisation an allocation may imply.  They also cannot hand us
+// a workspace they do not have.  For them the split-KV partial results live in the fixed array
+// below, which is part of the library image: every GPU that loads the library carries these
+// 16 MiB until the process exits, whether or not the entry point is ever called.
+//
+// All calls share the array and nothing clears it between calls: the reduce kernel reads only
+// the slots the decode kernel of the same call has just written, so stale contents are never
+// consumed and nothing needs to start at zero.  Two calls that overlap on the GPU (different
+// streams, or different host threads) race on it -- serialise them.
+// ------------------------------------------------------------------------------------------
+namespace cake {
+namespace gqa {
+
+constexpr size_t kNoAllocScratchBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_noalloc_mutex;
+static void* g_noalloc_address[kMaxDevices];     // DEVICE address of g_noalloc_scratch on each device
+static bool g_noalloc_ready[kMaxDevices];
+
+// In host code the name `g_noalloc_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address is asked for once per device, with that device current.
+static int noalloc_setup(int device, void** address) {
+  if (device < 0 || device >= kMaxDevices) return kErrBadArgument;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ready[device]) {
+    void* ptr = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (err != cudaSuccess) return int(err);
+    if (!ptr) return int(cudaErrorInvalidSymbol);
+    err = cudaFuncSetAttribute(gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (err != cudaSuccess) return int(err);
+    g_noalloc_address[device] = ptr;
+    g_noalloc_ready[device] = true;
+  }
+  *address = g_noalloc_address[device];
+  return 0;
+}
+
+}  // namespace gqa
+}  // namespace cake
+
+extern "C" size_t cake_b200_gqa_decode_noalloc_scratch_limit(void) { return cake::gqa::kNoAllocScratchBytes; }
+
+extern "C" int cake_b200_gqa_decode_noalloc(void** buffers, const cake_b200_gqa_decode_config* config, void* cuda_stream) {
+  using namespace cake;
+  if (!buffers || !config) return kErrBadArgument;
+  int device = 0;
+  if (int rc = require_blackwell(&device)) return rc;
+  if (!gqa_config_ok(*config)) return kErrBadArgument;
+  for (int i = 0; i < 9; ++i) {
+    if (!buffers[i]) return kErrBadArgument;
+    if (i <= 2 && (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
+  }
+  gqa::Params p;
+  p.q = static_cast<const __nv_bfloat16*>(buffers[0]);
+  p.k_cache = static_cast<const __nv_bfloat16*>(buffers[1]);
+  p.v_cache = static_cast<const __nv_bfloat16*>(buffers[2]);
+  p.kv_indptr = static_cast<const int*>(buffers[3]);
+  p.kv_indices = static_cast<const int*>(buffers[4]);
+  p.kv_last_page_len = static_cast<const int*>(buffers[5]);
+  p.sm_scale = static_cast<const float*>(buffers[6]);
+  p.out = static_cast<__nv_bfloat16*>(buffers[7]);
+  p.lse = static_cast<float*>(buffers[8]);
+  p.batch = int(config->batch);
+  p.hq = config->num_qo_heads;
+  p.hkv = config->num_kv_heads;
+  p.page_size = config->page_size;
+  if (p.batch == 0) return 0;
+  // Same chunking as the workspace variant; longer chunks (fewer partial results) if that is what
+  // it takes to fit the fixed scratch, and a refusal if even two chunks per sequence do not fit.
+  p.chunk = gqa::pick_chunk(*config, 148);
+  auto bytes_needed = [&](int chunk) {
+    const size_t splits = size_t((config->max_kv_len + chunk - 1) / chunk) + 1;
+    return size_t(p.batch) * splits * p.hq * (gqa::kD + 1) * sizeof(float);
+  };
+  while (bytes_needed(p.chunk) > gqa::kNoAllocScratchBytes && p.chunk < config->max_kv_len) p.chunk *= 2;
+  if (bytes_needed(p.chunk) > gqa::kNoAllocScratchBytes) return kErrWorkspace;   // batch * heads too large for 16 MiB
+  p.max_splits = int((config->max_kv_len + p.chunk - 1) / p.chunk) + 1;
+  void* scratch = nullptr;
+  if (int rc = gqa::noalloc_setup(device, &scratch)) return rc;
+  p.part_o = static_cast<float*>(scratch);
+  p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.hq * gqa::kD;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  gqa::gqa_decode_kernel<<<dim3(p.max_splits, p.hkv, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
+  gqa::gqa_reduce_kernel<<<dim3(p.hq, p.batch), gqa::kD, 0, s>>>(p);
+  return int(cudaGetLastError());
 }

@@ -30,7 +30,8 @@ def test_library_exports_every_declared_symbol():
 
 def test_every_entry_point_cites_the_reference_interface_it_replaces():
     for block in re.split(r"/\* -{20,}", HEADER)[1:]:
-        assert re.search(r"\b(src/open_cake_ir|corpus|tools)/[\w/.-]+(:\d+)?", block), block[:80]
+        cites = re.search(r"\b(src/open_cake_ir|corpus|tools)/[\w/.-]+(:\d+)?", block)
+        assert cites or "no counterpart in the reference" in block, block[:80]
 
 
 @pytest.mark.parametrize("stem", list(cake._lib.OPERATORS))
