@@ -303,8 +303,45 @@ def per_gpu_operators(peaks, iters=20, warmup=3):
     return rows
 
 
+def profile_case(name: str, launches: int = 3):
+    """Runs one small case of one operator a few times and exits: the command to put under ncu.
+    Cases keep the serving shapes' per-unit geometry (tokens per expert, heads, page size) with fewer
+    units, so that a capture holds a few GB at most and ends by itself."""
+    import open_cake_ir_b200 as cake
+    if name == "moe":            # 1024 tokens over 64 experts: 128 tokens per expert as at full size, 2.8 GB of weights
+        dev = cake.workloads.moe_inputs(tokens=1024, hidden=SHAPE["hidden"], inter=SHAPE["inter"], experts=64, local_experts=64,
+                                        routing="softmax", device="cuda", gen_device="cuda")
+        out = torch.empty((1024, SHAPE["hidden"]), dtype=torch.bfloat16, device="cuda")
+        op = cake.Fp8Moe(dev, out, experts=64, routing="softmax", act_mode="fp8")
+    elif name == "gemm":         # half the serving M
+        g = cake.workloads.block_scaled_gemm_inputs(4096, 4096, 7168, device="cuda", gen_device="cuda")
+        c = torch.empty((4096, 4096), dtype=torch.bfloat16, device="cuda")
+        op = cake.BlockScaledGemm(g["a"], g["sfa"], g["b"], g["sfb"], c)
+    elif name == "rmsnorm":
+        inputs, meta = cake.workloads.rmsnorm_inputs(4096, 4096, device="cuda", gen_device="cuda")
+        out = torch.empty_like(inputs["x"])
+        op = cake.RmsNorm(inputs["x"], inputs["weight"], out, meta["epsilon"])
+    elif name == "gqa":          # the serving batch and lengths (1.3 GB of cache)
+        dev, meta = cake.workloads.gqa_decode_inputs(device="cuda", gen_device="cuda")
+        out = torch.empty_like(dev["q"]); lse = torch.empty((64, 32), dtype=torch.float32, device="cuda")
+        op = cake.GqaPagedDecode(dev["q"], dev["k_cache"], dev["v_cache"], dev["kv_indptr"], dev["kv_indices"],
+                                 dev["kv_last_page_len"], dev["sm_scale"], out, lse, max_kv_len=meta["max_kv_len"])
+    elif name == "mla":          # the serving batch and lengths (0.3 GB of cache)
+        dev, meta = cake.workloads.mla_decode_inputs(device="cuda", gen_device="cuda")
+        out = torch.empty_like(dev["q_nope"]); lse = torch.empty((32, 128), dtype=torch.float32, device="cuda")
+        op = cake.MlaPagedDecode(dev["q_nope"], dev["q_pe"], dev["ckv_cache"], dev["kpe_cache"], dev["kv_indptr"],
+                                 dev["kv_indices"], dev["kv_last_page_len"], dev["sm_scale"], out, lse, max_kv_len=meta["max_kv_len"])
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    for _ in range(launches):
+        op.launch()
+    torch.cuda.synchronize()
+    if op.status():
+        raise SystemExit("a device-side wait ran out")
+
+
 # ------------------------------------------------------------------------------------------------
-CPU_SAMPLE = dict(tokens=256, local_experts=8, local_offset=0)
+CPU_SAMPLE = dict(tokens=2048, local_experts=32, local_offset=0)
 
 
 def cpu_reference_step(state):
@@ -367,7 +404,12 @@ def main():
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
     parser.add_argument("--skip-operators", action="store_true", help="time only the MoE layer")
     parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    parser.add_argument("--profile-case", default=None, choices=["moe", "gemm", "rmsnorm", "gqa", "mla"],
+                        help="launch one small case of one operator three times and exit (for ncu)")
     args = parser.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case)
+        return
     if args.impl == "reference":
         reference_arm(args)
         return

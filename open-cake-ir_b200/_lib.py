@@ -7,7 +7,10 @@ import ctypes
 from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
-LIBRARY_PATH = Path(__file__).resolve().parent / "libcake_b200.so"
+import os
+
+# CAKE_B200_LIBRARY points at another build of the same library (e.g. one with bounds checks).
+LIBRARY_PATH = Path(os.environ.get("CAKE_B200_LIBRARY") or Path(__file__).resolve().parent / "libcake_b200.so")
 
 
 class CakeError(RuntimeError):

@@ -13,7 +13,8 @@
 // Rows are TMEM lanes (UMMA M = 128), columns are TMEM columns (UMMA N = 256).  For every
 // 128-wide K block, four tcgen05.mma.kind::f8f6f4 (K = 32 each) write a FRESH partial product
 // into one of two TMEM accumulator stages; eight epilogue warps read that stage back
-// (tcgen05.ld), multiply it by the block's scales and add it to fp32 registers ("promotion"),
+// (tcgen05.ld), multiply it by the block's scales and add it to fp32 registers ("promotion",
+// packed two-wide fp32 FMAs),
 // which is what arbitrary fp32 1x128 / 128x128 scales need -- the hardware block-scaled kinds
 // only take power-of-two scales per 32 elements.  While the epilogue promotes block kb the
 // tensor core already works on block kb+1 in the other stage.  Operands arrive through a
@@ -22,6 +23,12 @@
 // fastest, so CTAs that share a weight tile run at the same time and the second reader hits L2.
 #pragma once
 #include "common.cuh"
+
+// Measurement aid, never set in the shipped build: 1 = the epilogue only hands the accumulator
+// stage back (no tensor-memory reads, results are garbage), 2 = it reads but does not accumulate.
+#ifndef CAKE_GEMM_PROBE
+#define CAKE_GEMM_PROBE 0
+#endif
 
 namespace cake {
 namespace gemm {
@@ -36,8 +43,13 @@ constexpr int kTmemColumns = kTmemStages * kBN;   // 512 = all of an SM's tensor
 constexpr int kBytesA = kBM * kBK;                // 16 KiB
 constexpr int kBytesB = kBN * kBK;                // 32 KiB
 constexpr int kStageBytes = kBytesA + kBytesB;
-constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = (2 + kEpilogueWarps) * 32;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kControlWarps = 4;                  // one warpgroup: warp 0 TMA, warp 1 MMA, warps 2-3 idle
+constexpr int kEpilogueWarps = 8;                 // two warpgroups: 2 column groups x 4 TMEM lane quadrants
+constexpr int kThreads = (kControlWarps + kEpilogueWarps) * 32;
+// Register budget moved between the warpgroups once the roles split (the kernel is launched with
+// 65536 / 384 -> 168 registers per thread): 128 control threads x 40 + 256 epilogue threads x 232 <= 65536.
+constexpr int kControlRegs = 40;
+constexpr int kEpilogueRegs = 232;
 constexpr int kMaxGroups = 512;
 
 enum Mode : int {
@@ -74,7 +86,7 @@ struct Shared {
   uint32_t tmem_base;
   int abort_flag;
   int tile_prefix[kMaxGroups + 1];     // m tiles before group g
-  float exchange[2][2][2][kBM];        // [item parity][term][column half][row] amax exchange for kGateUp
+  float exchange[2][2][2][kBM];        // [item parity][term][column group][row] amax exchange for kGateUp
 };
 
 struct Item {
@@ -124,7 +136,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tmem_alloc(&sh->tmem_base, kTmemColumns);
     tmem_relinquish();
   }
-  if (warp == 2) {   // m-tile prefix over groups (serial per lane chunk, then a warp scan)
+  if (warp == kControlWarps) {   // m-tile prefix over groups (serial per lane chunk, then a warp scan)
     int running = 0;
     for (int base = 0; base < p.groups; base += 32) {
       int g = base + lane;
@@ -150,6 +162,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_base = sh->tmem_base;
   volatile int* abort_flag = &sh->abort_flag;
 
+  if (warp < kControlWarps) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
   if (warp == 0) {
     // ------------------------------ TMA producer --------------------------------------
     if (elect_one()) {
@@ -210,16 +224,19 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs));
     // ------------------------------ epilogue / promotion ------------------------------
-    const int ew = warp - 2;
+    const int ew = warp - kControlWarps;
     const int quad = warp & 3;                 // TMEM lanes a warp may read: 32*(warp id % 4)
-    const int half = ew >> 2;                  // which half of the tile's columns
+    const int cg = ew >> 2;                    // column group 0..1
     const int r = quad * 32 + lane;            // row inside the tile
     const uint32_t lane_base = tmem_base + (uint32_t(quad * 32) << 16);
-    // Two 64-column segments per thread.
-    const int seg_col0 = (MODE == kGateUp) ? half * 64 : half * 128;
-    const int seg_col1 = (MODE == kGateUp) ? 128 + half * 64 : half * 128 + 64;
+    // Two 64-column segments per thread: gate/up takes 64 x1 columns and the matching 64 x2
+    // columns; the other modes take 128 consecutive columns.
+    const int seg_col0 = (MODE == kGateUp) ? cg * 64 : cg * 128;
+    const int seg_col1 = (MODE == kGateUp) ? 128 + cg * 64 : cg * 128 + 64;
     const int sfb_rows = p.b_rows_per_group / 128;
     uint32_t it = 0;
     int parity = 0;
@@ -233,106 +250,137 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         sfb_row0 = item.n_tile;
         sfb_row1 = p.n / 128 + item.n_tile;
       } else {
-        sfb_row0 = sfb_row1 = min(item.n_tile * 2 + half, sfb_rows - 1);
+        sfb_row0 = sfb_row1 = min(item.n_tile * 2 + cg, sfb_rows - 1);
       }
       const float* sfb0 = p.sfb + (size_t(item.group) * sfb_rows + sfb_row0) * p.b_k_blocks;
       const float* sfb1 = p.sfb + (size_t(item.group) * sfb_rows + sfb_row1) * p.b_k_blocks;
-      float acc[128];
+      float2 acc[64];                          // 128 fp32 accumulators as pairs for the two-wide FMA
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-      // scales of block 0, fetched before the first wait
-      int a_col = 0, b_col = 0;
-      float sa = __ldg(p.sfa + size_t(a_col) * p.row_capacity + row_c);
-      float sb0 = __ldg(sfb0 + b_col), sb1 = __ldg(sfb1 + b_col);
+      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+      // Scales travel kScaleAhead K blocks ahead of their use: an L2 round trip under a full TMA
+      // stream is longer than one K block, and a scale that arrives late stalls the whole promotion.
+      constexpr int kScaleAhead = 3;
+      float sa_q[kScaleAhead], sb0_q[kScaleAhead], sb1_q[kScaleAhead];
+      auto fetch = [&](int kb, float& sa, float& sb0, float& sb1) {
+        int a_col = kb, b_col = kb;
+        if (p.interleave_hi_lo) { a_col = (kb & 1) * (p.k_blocks >> 1) + (kb >> 1); b_col = kb >> 1; }
+        sa = __ldg(p.sfa + size_t(a_col) * p.row_capacity + row_c);
+        sb0 = __ldg(sfb0 + b_col);
+        sb1 = __ldg(sfb1 + b_col);
+      };
+#pragma unroll
+      for (int j = 0; j < kScaleAhead; ++j) {
+        sa_q[j] = sb0_q[j] = sb1_q[j] = 0.f;
+        if (j < p.k_blocks) fetch(j, sa_q[j], sb0_q[j], sb1_q[j]);
+      }
       for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
         const int t = it % kTmemStages;
-        const float s0 = sa * sb0, s1 = sa * sb1;
-        if (kb + 1 < p.k_blocks) {       // next block's scales travel while we wait
-          a_col = kb + 1; b_col = kb + 1;
-          if (p.interleave_hi_lo) { a_col = ((kb + 1) & 1) * (p.k_blocks >> 1) + ((kb + 1) >> 1); b_col = (kb + 1) >> 1; }
-          sa = __ldg(p.sfa + size_t(a_col) * p.row_capacity + row_c);
-          sb0 = __ldg(sfb0 + b_col); sb1 = __ldg(sfb1 + b_col);
-        }
+        const float s0 = sa_q[0] * sb0_q[0], s1 = sa_q[0] * sb1_q[0];
+#pragma unroll
+        for (int j = 0; j + 1 < kScaleAhead; ++j) { sa_q[j] = sa_q[j + 1]; sb0_q[j] = sb0_q[j + 1]; sb1_q[j] = sb1_q[j + 1]; }
+        if (kb + kScaleAhead < p.k_blocks) fetch(kb + kScaleAhead, sa_q[kScaleAhead - 1], sb0_q[kScaleAhead - 1], sb1_q[kScaleAhead - 1]);
         ok = mbar_wait(&sh->tmem_full[t], (it / kTmemStages) & 1, abort_flag, p.status, kStatusWaitTmemFull);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t stage_addr = lane_base + t * kBN;
+#if CAKE_GEMM_PROBE == 1
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->tmem_empty[t]);
+        acc[0].x += s0 + s1;
+        continue;
+#endif
+        // two round trips to tensor memory per K block, 64 columns each
+        float va[32], vb[32];
+        tmem_ld_32x32b_x32(stage_addr + seg_col0, va);
+        tmem_ld_32x32b_x32(stage_addr + seg_col0 + 32, vb);
+        tcgen05_wait_ld();
+#if CAKE_GEMM_PROBE == 2
+        acc[0].x += va[0] + vb[0] + s0;
+#else
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          const int col = (c < 2 ? seg_col0 : seg_col1) + (c & 1) * 32;
-          tmem_ld_32x32b_x32(stage_addr + col, v);
-          tcgen05_wait_ld();
-          if (c == 3) {                  // everything this warp needs has left tensor memory
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_empty[t]);
-          }
-          const float s = c < 2 ? s0 : s1;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(v[i], s, acc[c * 32 + i]);
+        for (int i = 0; i < 16; ++i) {
+          acc[i] = ffma2(make_float2(va[2 * i], va[2 * i + 1]), make_float2(s0, s0), acc[i]);
+          acc[16 + i] = ffma2(make_float2(vb[2 * i], vb[2 * i + 1]), make_float2(s0, s0), acc[16 + i]);
         }
+#endif
+        tmem_ld_32x32b_x32(stage_addr + seg_col1, va);
+        tmem_ld_32x32b_x32(stage_addr + seg_col1 + 32, vb);
+        tcgen05_wait_ld();
+        tcgen05_fence_before();            // everything this warp needs has left tensor memory
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->tmem_empty[t]);
+#if CAKE_GEMM_PROBE == 2
+        acc[1].x += va[0] + vb[0] + s1;
+#else
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          acc[32 + i] = ffma2(make_float2(va[2 * i], va[2 * i + 1]), make_float2(s1, s1), acc[32 + i]);
+          acc[48 + i] = ffma2(make_float2(vb[2 * i], vb[2 * i + 1]), make_float2(s1, s1), acc[48 + i]);
+        }
+#endif
       }
       if (!ok) break;
-      // rows past the group's end and, where N is an odd multiple of 128, the tile's second column half hold nothing
-      const bool valid = r < item.rows_valid && (MODE == kGateUp || item.n_tile * kBN + half * 128 < p.n);
+      // rows past the group's end and, where N is an odd multiple of 128, the tile's second column group hold nothing
+      const bool valid = r < item.rows_valid && (MODE == kGateUp || item.n_tile * kBN + cg * 128 < p.n);
 
       if (MODE == kDense) {
         if (valid) {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + half * 128;
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + cg * 128;
 #pragma unroll
-          for (int i = 0; i < 128; i += 8) {
+          for (int i = 0; i < 64; i += 4) {
             uint4 w;
-            w.x = pack_bf16x2(acc[i], acc[i + 1]); w.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
-            w.z = pack_bf16x2(acc[i + 4], acc[i + 5]); w.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
-            *reinterpret_cast<uint4*>(out + i) = w;
+            w.x = pack_bf16x2(acc[i].x, acc[i].y); w.y = pack_bf16x2(acc[i + 1].x, acc[i + 1].y);
+            w.z = pack_bf16x2(acc[i + 2].x, acc[i + 2].y); w.w = pack_bf16x2(acc[i + 3].x, acc[i + 3].y);
+            *reinterpret_cast<uint4*>(out + 2 * i) = w;
           }
         }
       } else if (MODE == kDown) {
         if (valid) {
           const float w = __ldg(p.row_weight + row);
-          float* out = reinterpret_cast<float*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + half * 128;
+          float* out = reinterpret_cast<float*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + cg * 128;
 #pragma unroll
-          for (int i = 0; i < 128; i += 4)
-            *reinterpret_cast<float4*>(out + i) = make_float4(acc[i] * w, acc[i + 1] * w, acc[i + 2] * w, acc[i + 3] * w);
+          for (int i = 0; i < 64; i += 2)
+            *reinterpret_cast<float4*>(out + 2 * i) = make_float4(acc[i].x * w, acc[i].y * w, acc[i + 1].x * w, acc[i + 1].y * w);
         }
       } else {
-        // SwiGLU on the 64 (x1, x2) pairs this thread holds, then e4m3 quantisation of the
-        // 128-wide group it shares with the thread of the same row in the other column half.
+        // SwiGLU on the 64 (x1, x2) pairs this thread holds, then e4m3 quantisation of the 128-wide
+        // group it shares with the thread of the same row in the other column group.
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float x2 = acc[64 + i];
-          const float a = acc[i] * (x2 / (1.f + __expf(-x2)));
-          acc[i] = a;
-          amax = fmaxf(amax, fabsf(a));
+        for (int i = 0; i < 32; ++i) {
+          const float g0 = acc[32 + i].x, g1 = acc[32 + i].y;
+          acc[i].x = acc[i].x * (g0 / (1.f + __expf(-g0)));
+          acc[i].y = acc[i].y * (g1 / (1.f + __expf(-g1)));
+          amax = fmaxf(amax, fmaxf(fabsf(acc[i].x), fabsf(acc[i].y)));
         }
         const int out_kb = p.n / 128;                      // K blocks of one term of the output
         const int terms = p.split_act ? 2 : 1;
-        uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out) + size_t(row) * (size_t(p.n) * terms) + item.n_tile * 128 + half * 64;
+        uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out) + size_t(row) * (size_t(p.n) * terms) + item.n_tile * 128 + cg * 64;
         for (int term = 0; term < terms; ++term) {
-          sh->exchange[parity][term][half][r] = amax;
+          sh->exchange[parity][term][cg][r] = amax;
           asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory");
-          const float group_amax = fmaxf(amax, sh->exchange[parity][term][half ^ 1][r]);
+          const float group_amax = fmaxf(amax, sh->exchange[parity][term][cg ^ 1][r]);
           const float scale = group_amax > 0.f ? group_amax / 448.f : 1.f;
           const float inv = 1.f / scale;
           uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 64; i += 4) packed[i >> 2] = pack_e4m3x4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
+          for (int i = 0; i < 32; i += 2) packed[i >> 1] = pack_e4m3x4(acc[i].x * inv, acc[i].y * inv, acc[i + 1].x * inv, acc[i + 1].y * inv);
           if (valid) {
             uint4* dst = reinterpret_cast<uint4*>(out_base + size_t(term) * p.n);
 #pragma unroll
             for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-            if (half == 0) p.out_scale[size_t(term * out_kb + item.n_tile) * p.row_capacity + row] = scale;
+            if (cg == 0) p.out_scale[size_t(term * out_kb + item.n_tile) * p.row_capacity + row] = scale;
           }
           if (term + 1 < terms) {        // residual after the first term becomes the value to quantise
             amax = 0.f;
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-              const uint8_t q = uint8_t(packed[i >> 2] >> ((i & 3) * 8));
-              const float rem = acc[i] - e4m3_to_float(q) * scale;
-              acc[i] = rem;
-              amax = fmaxf(amax, fabsf(rem));
+            for (int i = 0; i < 32; ++i) {
+              const uint32_t word = packed[i >> 1];
+              const float r0 = acc[i].x - e4m3_to_float(uint8_t(word >> ((i & 1) * 16))) * scale;
+              const float r1 = acc[i].y - e4m3_to_float(uint8_t(word >> ((i & 1) * 16 + 8))) * scale;
+              acc[i] = make_float2(r0, r1);
+              amax = fmaxf(amax, fmaxf(fabsf(r0), fabsf(r1)));
             }
           }
         }
