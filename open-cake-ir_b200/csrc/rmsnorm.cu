@@ -11,7 +11,7 @@
 namespace cake {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kMaxThreads = 512;
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float* v) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -33,41 +33,77 @@ __device__ __forceinline__ void st_stream(uint4* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// VPT = 16-byte vectors per thread; a row has width/8 vectors, at most VPT*kThreads.
-template <int VPT, bool RESIDUAL>
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ float sum_squares8(const uint4& raw) {
+  float v[8];
+  unpack8(raw, v);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+  return ss;
+}
+
+// VPT = 16-byte vectors per thread; a row has width/8 vectors, at most VPT*kThreads.  The row and
+// the weights stay in registers as the packed bf16 they arrived as (4 registers per vector) and
+// are unpacked where they are used; with one vector per thread the kernel fits 40 registers, so an
+// SM holds 1536 threads, each with the next row's vector already in flight (48 KiB of loads per SM).
+template <int kThreads, int VPT, bool RESIDUAL>
+__global__ void __launch_bounds__(kThreads, VPT == 1 ? 1536 / kThreads : ((2048 / kThreads) / VPT > 0 ? (2048 / kThreads) / VPT : 1))
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
                int rows, int width, float eps) {
   __shared__ float partial[2][kThreads / 32];
   const int vectors = width >> 3;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float w[VPT][8];
+  uint4 w[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * kThreads;
-    if (idx < vectors) unpack8(__ldg(reinterpret_cast<const uint4*>(weight) + idx), w[i]);
+    w[i] = idx < vectors ? __ldg(reinterpret_cast<const uint4*>(weight) + idx) : make_uint4(0, 0, 0, 0);
   }
   const float inv_width = 1.f / float(width);
   int flip = 0;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
-    const uint4* src = reinterpret_cast<const uint4*>(x + size_t(row) * width);
-    float v[VPT][8];
-    float ss = 0.f;
+  // The next row's loads are issued before the current row is reduced and stored, so a CTA
+  // always has a row in flight while it works on another.
+  uint4 ahead[VPT];
+  if (blockIdx.x < rows) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * kThreads;
-      if (idx < vectors) {
-        unpack8(ld_stream(src + idx), v[i]);
-        if (RESIDUAL) {
-          float r[8];
-          unpack8(ld_stream(reinterpret_cast<const uint4*>(residual + size_t(row) * width) + idx), r);
+      ahead[i] = idx < vectors ? ld_stream(reinterpret_cast<const uint4*>(x + size_t(blockIdx.x) * width) + idx)
+                               : make_uint4(0, 0, 0, 0);
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
+    uint4 raw[VPT];
+    float z[RESIDUAL ? VPT : 1][8];        // the fused variant must keep fp32(x + residual)
+    float ss = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[i][j] += r[j];
-        }
+    for (int i = 0; i < VPT; ++i) raw[i] = ahead[i];
+    const int next = row + gridDim.x;
+    if (next < rows) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+      for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * kThreads;
+        if (idx < vectors) ahead[i] = ld_stream(reinterpret_cast<const uint4*>(x + size_t(next) * width) + idx);
       }
+    }
+    if (RESIDUAL) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int idx = threadIdx.x + i * kThreads;
+        float r[8];
+        unpack8(raw[i], z[RESIDUAL ? i : 0]);
+        unpack8(idx < vectors ? ld_stream(reinterpret_cast<const uint4*>(residual + size_t(row) * width) + idx)
+                              : make_uint4(0, 0, 0, 0), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          z[RESIDUAL ? i : 0][j] += r[j];
+          ss = fmaf(z[RESIDUAL ? i : 0][j], z[RESIDUAL ? i : 0][j], ss);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) ss += sum_squares8(raw[i]);
     }
     ss = warp_sum(ss);
     if (lane == 0) partial[flip][warp] = ss;
@@ -81,11 +117,19 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * kThreads;
       if (idx < vectors) {
+        float v[8], wf[8];
+        if (RESIDUAL) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = z[RESIDUAL ? i : 0][j];
+        } else {
+          unpack8(raw[i], v);
+        }
+        unpack8(w[i], wf);
         uint4 o;
-        o.x = pack_bf16x2(v[i][0] * inverse * w[i][0], v[i][1] * inverse * w[i][1]);
-        o.y = pack_bf16x2(v[i][2] * inverse * w[i][2], v[i][3] * inverse * w[i][3]);
-        o.z = pack_bf16x2(v[i][4] * inverse * w[i][4], v[i][5] * inverse * w[i][5]);
-        o.w = pack_bf16x2(v[i][6] * inverse * w[i][6], v[i][7] * inverse * w[i][7]);
+        o.x = pack_bf16x2(v[0] * inverse * wf[0], v[1] * inverse * wf[1]);
+        o.y = pack_bf16x2(v[2] * inverse * wf[2], v[3] * inverse * wf[3]);
+        o.z = pack_bf16x2(v[4] * inverse * wf[4], v[5] * inverse * wf[5]);
+        o.w = pack_bf16x2(v[6] * inverse * wf[6], v[7] * inverse * wf[7]);
         st_stream(dst + idx, o);
       }
     }
@@ -102,12 +146,12 @@ struct Handle {
   int grid;
 };
 
-template <int VPT>
+template <int kThreads, int VPT>
 void launch(const Handle* h, cudaStream_t stream) {
   if (h->residual)
-    rmsnorm_kernel<VPT, true><<<h->grid, kThreads, 0, stream>>>(h->x, h->residual, h->weight, h->out, h->rows, h->width, h->eps);
+    rmsnorm_kernel<kThreads, VPT, true><<<h->grid, kThreads, 0, stream>>>(h->x, h->residual, h->weight, h->out, h->rows, h->width, h->eps);
   else
-    rmsnorm_kernel<VPT, false><<<h->grid, kThreads, 0, stream>>>(h->x, nullptr, h->weight, h->out, h->rows, h->width, h->eps);
+    rmsnorm_kernel<kThreads, VPT, false><<<h->grid, kThreads, 0, stream>>>(h->x, nullptr, h->weight, h->out, h->rows, h->width, h->eps);
 }
 
 }  // namespace
@@ -125,7 +169,7 @@ extern "C" int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_
     if ((!buffers[i] && !may_be_empty) || (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
   }
   if (config->rows < 0 || config->rows > INT32_MAX || config->width <= 0 || (config->width & 7) ||
-      config->width > 8 * 8 * kThreads || !(config->epsilon >= 0.f))
+      config->width > 8 * 8 * kMaxThreads || !(config->epsilon >= 0.f))
     return kErrBadArgument;
   auto* h = new (std::nothrow) Handle;
   if (!h) return int(cudaErrorMemoryAllocation);
@@ -139,9 +183,11 @@ extern "C" int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_
   h->width = int(config->width);
   h->eps = config->epsilon;
   const int vectors = h->width / 8;
-  const int need = (vectors + kThreads - 1) / kThreads;
-  h->vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-  h->grid = h->rows < 1 ? 1 : (h->rows < sm_count(device) * 64 ? h->rows : sm_count(device) * 64);
+  // shape class: 0 = 256 threads x 1 vector; 1..4 = 512 threads x 1, 2, 4, 8 vectors
+  h->vpt = vectors <= 256 ? 0 : vectors <= 512 ? 1 : vectors <= 1024 ? 2 : vectors <= 2048 ? 3 : 4;
+  // persistent CTAs: as many as are resident at once, each walking rows with a stride of the grid
+  const int resident = sm_count(device) * (h->vpt == 0 ? 6 : h->vpt == 1 ? 3 : h->vpt == 2 ? 2 : 1);
+  h->grid = h->rows < 1 ? 1 : (h->rows < resident ? h->rows : resident);
   *handle_out = h;
   return 0;
 }
@@ -156,10 +202,11 @@ extern "C" int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream) {
   if (h->rows == 0) return 0;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
   switch (h->vpt) {
-    case 1: launch<1>(h, stream); break;
-    case 2: launch<2>(h, stream); break;
-    case 4: launch<4>(h, stream); break;
-    default: launch<8>(h, stream); break;
+    case 0: launch<256, 1>(h, stream); break;
+    case 1: launch<512, 1>(h, stream); break;
+    case 2: launch<512, 2>(h, stream); break;
+    case 3: launch<512, 4>(h, stream); break;
+    default: launch<512, 8>(h, stream); break;
   }
   return int(cudaGetLastError());
 }
