@@ -222,14 +222,13 @@ def moe_parallel(steps, warmup, world, rank):
     dev = cake.workloads.moe_inputs(tokens=t_local, hidden=SHAPE["hidden"], inter=SHAPE["inter"], experts=SHAPE["experts"],
                                     local_experts=e_local, local_offset=rank * e_local, routing="softmax", device="cuda",
                                     gen_device="cuda", first_token=rank * t_local, total_tokens=SHAPE["tokens"])
-    route_factory, local_layer = ep.native_layer(dev, capacity=SHAPE["tokens"], experts=SHAPE["experts"])
-    layer = ep.ExpertParallelMoe(experts=SHAPE["experts"], top_k=SHAPE["top_k"], hidden=SHAPE["hidden"],
-                                 capacity=SHAPE["tokens"], route=route_factory("softmax"), local_layer=local_layer)
-    args = [dev[k] for k in ("routing_logits", "routing_bias", "routed_scaling_factor", "hidden_states", "hidden_states_scale")]
+    layer = ep.NativeExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                                       dev["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"],
+                                       routing="softmax")
     result = {}
 
     def step():
-        result["out"] = layer.forward(*args)
+        result["out"] = layer.forward()
 
     with ClockSampler(torch.cuda.current_device()) as clocks:
         ms = time_steps(step, steps, warmup, world)
@@ -247,7 +246,8 @@ def moe_parallel(steps, warmup, world, rank):
     e2e_ms = time_steps(e2e_step, steps, warmup, world)
     flops = cake.workloads.moe_flops(SHAPE["tokens"], SHAPE["hidden"], SHAPE["inter"])
     return {"ms": ms, "flops": flops, "clocks": clocks.summary(), "e2e_ms": e2e_ms, "h2d": h2d * world, "d2h": d2h * world,
-            "launches": 9 * steps, "rows_sent_rank0": sum(layer.last_counts[0])}
+            "launches": layer.launches_per_step * steps,
+            "rows_sent_rank0": int((layer.slot_of >= 0).sum().item())}
 
 
 def per_gpu_operators(peaks, iters=20, warmup=3):

@@ -215,6 +215,33 @@ int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_decode_confi
 int cake_b200_mla_decode_launch(void* handle, void* cuda_stream);
 int cake_b200_mla_decode_destroy(void* handle);
 
+/* ------------------------------------------------------------------------------------------
+ * Expert-parallel exchange around the rank-local MoE layer.  The reference holds only the rank-local view
+ * (a rank owns experts [local_expert_offset, +local_experts) and other pairs contribute nothing,
+ * src/open_cake_ir/tasks/solx_fib/moe.py:139-146); these kernels are the data movement that joins R such ranks.
+ * Rank r owns experts [r*experts/world, (r+1)*experts/world).  A token goes once to every rank that owns one
+ * of its experts, as a packed row of cake_b200_ep_row_bytes() = H + 4*H/128 + 8*top_k bytes
+ * (e4m3 row | K-block scales | expert ids | route weights).  Every rank exchanges exactly `capacity` rows with
+ * every peer (unused rows carry expert id -1), so no size ever has to reach the host.
+ * buffers: 0 expert_ids int32 [T,top_k], 1 route_weights fp32 [T,top_k], 2 hidden_states e4m3 [T,H],
+ *   3 hidden_states_scale fp32 [H/128,T] (inputs, this rank's tokens); 4 slot_of int32 [T,world] (scratch);
+ *   5 send u8 [world,capacity,row_bytes] (written by stage 0); 6 recv u8 [world,capacity,row_bytes] (filled by the
+ *   caller's all-to-all of `send`); 7..10 the rank-local layer's inputs written by stage 1: hidden e4m3
+ *   [world*capacity,H], scales fp32 [H/128,world*capacity], expert_ids int32 and route_weights fp32
+ *   [world*capacity,top_k]; 11 returned bf16 [world,capacity,H] (filled by the caller's reverse all-to-all of the
+ *   layer's output); 12 output bf16 [T,H] (written by stage 2: partial rows added in rank order in fp32).
+ * stages: 0 plan + pack, 1 unpack, 2 reduce.  H % 512 == 0 (packed rows stay 16-byte aligned).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t tokens;   /* tokens of this rank */
+  int64_t capacity; /* rows exchanged with each peer; >= tokens */
+  int32_t hidden, top_k, world, experts;
+} cake_b200_ep_config;
+size_t cake_b200_ep_row_bytes(const cake_b200_ep_config* config);
+int cake_b200_ep_exchange_create(void** buffers, const cake_b200_ep_config* config, void** handle_out);
+int cake_b200_ep_exchange_launch_stage(void* handle, int stage, void* cuda_stream);
+int cake_b200_ep_exchange_destroy(void* handle);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,6 +52,11 @@ class MoeConfig(Structure):
                 ("routing_mode", c_int32), ("act_mode", c_int32), ("external_routing", c_int32)]
 
 
+class EpConfig(Structure):
+    _fields_ = [("tokens", c_int64), ("capacity", c_int64), ("hidden", c_int32), ("top_k", c_int32),
+                ("world", c_int32), ("experts", c_int32)]
+
+
 class GqaDecodeConfig(Structure):
     _fields_ = [("batch", c_int64), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32), ("head_dim", c_int32),
                 ("page_size", c_int32), ("max_kv_len", c_int64)]
@@ -74,7 +79,9 @@ OPERATORS = {
 }
 # every symbol include/cake_b200.h declares
 EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
-            "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit"]
+            "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit",
+            "cake_b200_ep_row_bytes", "cake_b200_ep_exchange_create", "cake_b200_ep_exchange_launch_stage",
+            "cake_b200_ep_exchange_destroy"]
            + [f"cake_b200_{stem}_{verb}" for stem in OPERATORS for verb in ("create", "launch", "destroy")]
            + [f"cake_b200_{stem}_workspace_bytes" for stem, (_, ws) in OPERATORS.items() if ws])
 
@@ -96,6 +103,11 @@ def library() -> ctypes.CDLL:
         lib.cake_b200_gqa_decode_noalloc.argtypes = [POINTER(c_void_p), POINTER(GqaDecodeConfig), c_void_p]
         lib.cake_b200_gqa_decode_noalloc.restype = c_int
         lib.cake_b200_gqa_decode_noalloc_scratch_limit.restype = c_size_t
+        lib.cake_b200_ep_row_bytes.argtypes = [POINTER(EpConfig)]
+        lib.cake_b200_ep_row_bytes.restype = c_size_t
+        lib.cake_b200_ep_exchange_create.argtypes = [POINTER(c_void_p), POINTER(EpConfig), POINTER(c_void_p)]
+        lib.cake_b200_ep_exchange_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
+        lib.cake_b200_ep_exchange_destroy.argtypes = [c_void_p]
         for stem, (config, has_ws) in OPERATORS.items():
             create = getattr(lib, f"cake_b200_{stem}_create")
             create.argtypes = [POINTER(c_void_p), POINTER(config), POINTER(c_void_p)]

@@ -16,7 +16,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBRARY = HERE / "libcake_b200.so"
-SOURCES = ("rmsnorm.cu", "gemm_fp8.cu", "moe.cu", "decode_gqa.cu", "decode_mla.cu", "misc.cu")
+SOURCES = ("rmsnorm.cu", "gemm_fp8.cu", "moe.cu", "decode_gqa.cu", "decode_mla.cu", "ep.cu", "misc.cu")
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v")
 

@@ -56,7 +56,7 @@ enum Mode : int {
   kDense = 0,        // C bf16 [M, N]
   kGateUp = 1,       // grouped GEMM1: x1 = cols [0,128), x2 = cols [128,256) of the tile;
                      // out = e4m3(x1 * silu(x2)) + per-(row,128) scale  (optionally hi+lo split)
-  kDown = 2,         // grouped GEMM2: out fp32 [rows, N] = acc * route weight of the row
+  kDown = 2,         // grouped GEMM2: out bf16 [rows, N] = acc * route weight of the row
 };
 
 struct Params {
@@ -338,10 +338,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       } else if (MODE == kDown) {
         if (valid) {
           const float w = __ldg(p.row_weight + row);
-          float* out = reinterpret_cast<float*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + cg * 128;
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + cg * 128;
 #pragma unroll
-          for (int i = 0; i < 64; i += 2)
-            *reinterpret_cast<float4*>(out + 2 * i) = make_float4(acc[i].x * w, acc[i].y * w, acc[i + 1].x * w, acc[i + 1].y * w);
+          for (int i = 0; i < 64; i += 4) {
+            uint4 v;
+            v.x = pack_bf16x2(acc[i].x * w, acc[i].y * w); v.y = pack_bf16x2(acc[i + 1].x * w, acc[i + 1].y * w);
+            v.z = pack_bf16x2(acc[i + 2].x * w, acc[i + 2].y * w); v.w = pack_bf16x2(acc[i + 3].x * w, acc[i + 3].y * w);
+            *reinterpret_cast<uint4*>(out + 2 * i) = v;
+          }
         }
       } else {
         // SwiGLU on the 64 (x1, x2) pairs this thread holds, then e4m3 quantisation of the 128-wide

@@ -178,28 +178,49 @@ scan_kernel(const int* __restrict__ counts, int* __restrict__ offsets, int local
   if (threadIdx.x == 0) offsets[local_experts] = carry;
 }
 
-// One warp per local expert walks all pairs in ascending order; ballots give the stable rank.
-__global__ void __launch_bounds__(128)
+// One CTA of eight warps per local expert.  Each warp owns a contiguous eighth of the pairs: a first
+// pass counts its matches, a prefix over the eight warps gives every warp its starting position, a
+// second pass places the pairs by ballot rank -- ascending pair order inside the expert, so the
+// permutation is the stable sort by expert.  Eight loads per lane are in flight per step.
+constexpr int kPlaceWarps = 8;
+constexpr int kPlaceStep = 256;      // pairs one warp looks at per step
+__global__ void __launch_bounds__(kPlaceWarps * 32)
 place_kernel(const int* __restrict__ expert_ids, const int* __restrict__ offset_ptr,
              const int* __restrict__ offsets, int* __restrict__ sorted_pairs, int* __restrict__ inv_perm,
              int pairs, int local_experts) {
-  const int lane = threadIdx.x & 31;
-  const int e = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (e >= local_experts) return;
+  __shared__ int warp_count[kPlaceWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.x;
   const int want = e + __ldg(offset_ptr);
-  int cursor = offsets[e];
-  if (offsets[e + 1] == cursor) return;
+  const int first = offsets[e];
+  if (offsets[e + 1] == first) return;
+  const int per_warp = ((pairs + kPlaceWarps - 1) / kPlaceWarps + kPlaceStep - 1) / kPlaceStep * kPlaceStep;
+  const int begin = warp * per_warp, end = min(pairs, begin + per_warp);
   const uint32_t below = (1u << lane) - 1u;
-  for (int base = 0; base < pairs; base += 128) {
-    // lane handles pairs base + 32*i + lane, i = 0..3, so ballots keep ascending pair order
-    int ids[4];
+  int count = 0;
+  for (int base = begin; base < end; base += kPlaceStep) {
+    int ids[kPlaceStep / 32];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < kPlaceStep / 32; ++i) {
       const int p = base + 32 * i + lane;
-      ids[i] = p < pairs ? __ldg(expert_ids + p) : -1;
+      ids[i] = p < end ? __ldg(expert_ids + p) : -1;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < kPlaceStep / 32; ++i) count += __popc(__ballot_sync(0xffffffffu, ids[i] == want));
+  }
+  if (lane == 0) warp_count[warp] = count;
+  __syncthreads();
+  int cursor = first;
+  for (int w = 0; w < warp; ++w) cursor += warp_count[w];
+  for (int base = begin; base < end; base += kPlaceStep) {
+    int ids[kPlaceStep / 32];
+#pragma unroll
+    for (int i = 0; i < kPlaceStep / 32; ++i) {
+      const int p = base + 32 * i + lane;      // lane-contiguous loads keep ballots in ascending pair order
+      ids[i] = p < end ? __ldg(expert_ids + p) : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < kPlaceStep / 32; ++i) {
       const bool hit = ids[i] == want;
       const uint32_t mask = __ballot_sync(0xffffffffu, hit);
       if (hit) {
@@ -235,27 +256,33 @@ gather_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hidd
   }
 }
 
-// out[t,:] = bf16( sum over the token's local slots, in slot order, of y[inv_perm[t,slot],:] ).
+// out[t,:] = bf16( fp32 sum over the token's local slots, in slot order, of the bf16 rows y[inv_perm[t,slot],:] ).
 __global__ void __launch_bounds__(256)
-combine_kernel(const float* __restrict__ y, const int* __restrict__ inv_perm, __nv_bfloat16* __restrict__ out,
+combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv_perm, __nv_bfloat16* __restrict__ out,
                int hidden_width, int top_k) {
   const int token = blockIdx.x;
   __shared__ int rows[32];
   if (threadIdx.x < top_k) rows[threadIdx.x] = inv_perm[size_t(token) * top_k + threadIdx.x];
   __syncthreads();
-  for (int c = threadIdx.x * 4; c < hidden_width; c += blockDim.x * 4) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = threadIdx.x * 8; c < hidden_width; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < top_k; ++s) {
       const int row = rows[s];
       if (row >= 0) {
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(y + size_t(row) * hidden_width + c));
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + size_t(row) * hidden_width + c));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
       }
     }
-    uint2 o;
-    o.x = pack_bf16x2(acc.x, acc.y);
-    o.y = pack_bf16x2(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(out + size_t(token) * hidden_width + c) = o;
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + size_t(token) * hidden_width + c) = o;
   }
 }
 
@@ -297,7 +324,7 @@ inline int launch_permute(const PermuteArgs& a, cudaStream_t s) {
   const int scan_threads = a.local_experts >= 1024 ? 1024 : ((a.local_experts + 31) / 32) * 32;
   scan_kernel<<<1, scan_threads, 0, s>>>(a.counts, a.offsets, a.local_experts);
   if (a.pairs > 0)
-    place_kernel<<<(a.local_experts + 3) / 4, 128, 0, s>>>(a.expert_ids, a.local_offset, a.offsets, a.sorted_pairs,
+    place_kernel<<<a.local_experts, kPlaceWarps * 32, 0, s>>>(a.expert_ids, a.local_offset, a.offsets, a.sorted_pairs,
                                                           a.inv_perm, a.pairs, a.local_experts);
   return int(cudaGetLastError());
 }
@@ -338,7 +365,7 @@ inline Layout make_layout(const cake_b200_moe_config& c) {
   l.sx_perm = take(size_t(c.hidden / 128) * l.capacity * 4);
   l.act = take(size_t(l.capacity) * c.intermediate * l.terms);
   l.act_scale = take(size_t(c.intermediate / 128) * l.terms * l.capacity * 4);
-  l.y = take(size_t(l.capacity) * c.hidden * 4);
+  l.y = take(size_t(l.capacity) * c.hidden * 2);
   l.total = at;
   return l;
 }
@@ -556,7 +583,7 @@ static int moe_launch_stage(cake::moe::MoeHandle* h, int stage, cudaStream_t s) 
       gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_b2, h->p2);
       break;
     case 3:
-      moe::combine_kernel<<<tokens, 256, 0, s>>>(reinterpret_cast<const float*>(h->ws + l.y), pa.inv_perm, h->output,
+      moe::combine_kernel<<<tokens, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(h->ws + l.y), pa.inv_perm, h->output,
                                                  c.hidden, c.top_k);
       break;
     default:

@@ -151,3 +151,92 @@ def native_layer(weights: dict, *, capacity: int, experts: int, top_k: int = 8, 
         return out
 
     return route_factory, local_layer
+
+
+class NativeExpertParallelMoe:
+    """The same layer on the native exchange kernels (``cake_b200_ep_exchange_*``): every shape is
+    static -- each rank exchanges ``tokens`` rows with every peer, unused rows carry expert id -1 --
+    so a step is kernel launches and two equal-split all-to-alls with no host synchronisation.
+
+    ``weights`` holds this rank's ``gemm1_weights``, ``gemm1_weights_scale``, ``gemm2_weights``,
+    ``gemm2_weights_scale``, ``local_expert_offset`` and ``routed_scaling_factor``; the token inputs
+    are bound at construction (their device buffers are reused every step)."""
+
+    def __init__(self, weights: dict, routing_logits, routing_bias, hidden_states, hidden_states_scale, *,
+                 experts: int, top_k: int = 8, routing: str = "softmax", n_group: int = 8, topk_group: int = 4,
+                 act_mode: str = "fp8", group=None):
+        import ctypes
+
+        from . import _lib, ops
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        dev = hidden_states.device
+        self.device = dev
+        tokens, hidden = hidden_states.shape
+        self.tokens, self.hidden, self.top_k = tokens, hidden, top_k
+        cap = tokens
+        rows = self.world * cap
+        cfg = _lib.EpConfig(tokens, cap, hidden, top_k, self.world, experts)
+        width = int(_lib.library().cake_b200_ep_row_bytes(ctypes.byref(cfg)))
+        if width == 0:
+            raise ValueError("unsupported expert-parallel configuration (hidden must be a multiple of 512)")
+        i32, f32 = torch.int32, torch.float32
+        self.ids = torch.empty((tokens, top_k), dtype=i32, device=dev)
+        self.route_weights = torch.empty((tokens, top_k), dtype=f32, device=dev)
+        self.slot_of = torch.empty((tokens, self.world), dtype=i32, device=dev)
+        self.send = torch.zeros((self.world, cap, width), dtype=torch.uint8, device=dev)
+        self.recv = torch.zeros((self.world, cap, width), dtype=torch.uint8, device=dev)
+        self.recv_hidden = torch.zeros((rows, hidden), dtype=torch.float8_e4m3fn, device=dev)
+        self.recv_scale = torch.zeros((hidden // 128, rows), dtype=f32, device=dev)
+        self.recv_ids = torch.full((rows, top_k), -1, dtype=i32, device=dev)
+        self.recv_weights = torch.zeros((rows, top_k), dtype=f32, device=dev)
+        self.partial = torch.empty((rows, hidden), dtype=torch.bfloat16, device=dev)
+        self.returned = torch.empty((self.world, cap, hidden), dtype=torch.bfloat16, device=dev)
+        self.output = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        self.router = ops.MoeRouting(routing_logits, routing_bias, weights["routed_scaling_factor"], self.ids,
+                                     self.route_weights, top_k=top_k, n_group=n_group, topk_group=topk_group, mode=routing)
+        layer_inputs = dict(weights)
+        layer_inputs.update(expert_ids=self.recv_ids, route_weights=self.recv_weights, hidden_states=self.recv_hidden,
+                            hidden_states_scale=self.recv_scale)
+        self.layer = ops.Fp8Moe(layer_inputs, self.partial, experts=experts, top_k=top_k, act_mode=act_mode,
+                                external_routing=True)
+        buffers = [self.ids, self.route_weights, hidden_states, hidden_states_scale, self.slot_of, self.send, self.recv,
+                   self.recv_hidden, self.recv_scale, self.recv_ids, self.recv_weights, self.returned, self.output]
+        self._keep = buffers
+        pointers = (ctypes.c_void_p * len(buffers))(*[t.data_ptr() for t in buffers])
+        self._handle = ctypes.c_void_p()
+        with torch.cuda.device(dev):
+            code = _lib.library().cake_b200_ep_exchange_create(pointers, ctypes.byref(cfg), ctypes.byref(self._handle))
+        if code:
+            raise _lib.CakeError("cake_b200_ep_exchange_create", code)
+        self._lib = _lib
+        # kernels of this library launched per step: routing 1, exchange 4, rank-local layer 7
+        self.launches_per_step = 12
+
+    def _stage(self, stage: int):
+        code = self._lib.library().cake_b200_ep_exchange_launch_stage(self._handle, stage, torch.cuda.current_stream().cuda_stream)
+        if code:
+            raise self._lib.CakeError("cake_b200_ep_exchange_launch_stage", code)
+
+    def forward(self) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            self.router.launch()
+            self._stage(0)
+            if self.world == 1:
+                self.recv.copy_(self.send)
+            else:
+                dist.all_to_all_single(self.recv, self.send, group=self.group)
+            self._stage(1)
+            self.layer.launch()
+            if self.world == 1:
+                self.returned.copy_(self.partial.view_as(self.returned))
+            else:
+                dist.all_to_all_single(self.returned, self.partial.view_as(self.returned), group=self.group)
+            self._stage(2)
+        return self.output
+
+    def close(self):
+        if self._handle.value:
+            self._lib.library().cake_b200_ep_exchange_destroy(self._handle)
+            import ctypes
+            self._handle = ctypes.c_void_p()

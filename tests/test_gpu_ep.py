@@ -1,0 +1,81 @@
+"""GPU test of the expert-parallel layer on two B200s (skipped on a single-GPU box): tokens and
+experts sharded over two NCCL ranks with all-to-all dispatch and combine must reproduce the
+single-GPU native layer over all tokens and experts.  Partial rows travel as bf16 and are added in
+fp32, so the comparison is at the bf16 tolerance (rtol 2e-2 / atol 2e-2, Frobenius <= 1e-2)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import open_cake_ir_b200 as cake
+from open_cake_ir_b200 import ep
+from oracle import compare
+
+pytestmark = pytest.mark.gpu
+SHAPE = dict(hidden=1024, inter=512, experts=32)
+TOKENS = 512
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, results, native):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        t_local, e_local = TOKENS // world, SHAPE["experts"] // world
+        dev = cake.workloads.moe_inputs(tokens=t_local, **SHAPE, local_experts=e_local, local_offset=rank * e_local,
+                                        routing="softmax", device=f"cuda:{rank}", gen_device="cpu",
+                                        first_token=rank * t_local, total_tokens=TOKENS)
+        args = [dev[k] for k in ("routing_logits", "routing_bias", "routed_scaling_factor", "hidden_states", "hidden_states_scale")]
+        if native:
+            layer = ep.NativeExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                                               dev["hidden_states_scale"], experts=SHAPE["experts"], routing="softmax")
+            for _ in range(2):      # twice: buffers are reused between steps
+                out = layer.forward()
+        else:
+            route_factory, local_layer = ep.native_layer(dev, capacity=TOKENS, experts=SHAPE["experts"], device=f"cuda:{rank}")
+            layer = ep.ExpertParallelMoe(experts=SHAPE["experts"], top_k=8, hidden=SHAPE["hidden"], capacity=TOKENS,
+                                         route=route_factory("softmax"), local_layer=local_layer, device=f"cuda:{rank}")
+            for _ in range(2):
+                out = layer.forward(*args)
+        torch.cuda.synchronize()
+        results[rank] = out.cpu()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("native", [True, False], ids=["native-exchange", "torch-exchange"])
+def test_two_rank_layer_equals_single_gpu_layer(native):
+    world = 2
+    results = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), results, native), nprocs=world, join=True)
+    whole = cake.workloads.moe_inputs(tokens=TOKENS, **SHAPE, local_experts=SHAPE["experts"], local_offset=0,
+                                      routing="softmax", device="cuda:0", gen_device="cpu")
+    want = cake.fp8_moe(whole, experts=SHAPE["experts"], routing="softmax", act_mode="fp8").cpu()
+    got = torch.cat([results[r] for r in range(world)])
+    assert compare.rel_frobenius(got, want) <= 1e-2
+    ok, bad, err = compare.compare(got, want, atol=2e-2, rtol=2e-2)
+    assert ok, f"{bad} mismatches, max abs err {err}"
+
+
+def test_single_rank_exchange_is_the_identity():
+    """World size 1 (runs on any GPU box): plan, pack, unpack and reduce around the rank-local layer must
+    reproduce the plain layer bit for bit, since one bf16 partial per token is added to nothing."""
+    dev = cake.workloads.moe_inputs(tokens=200, **SHAPE, local_experts=SHAPE["experts"], local_offset=0, routing="softmax",
+                                    device="cuda", gen_device="cpu")
+    want = cake.fp8_moe(dev, experts=SHAPE["experts"], routing="softmax", act_mode="fp8")
+    layer = ep.NativeExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                                       dev["hidden_states_scale"], experts=SHAPE["experts"], routing="softmax")
+    got = layer.forward()
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert int((layer.slot_of.cpu()[:, 0] != torch.arange(200)).sum()) == 0

@@ -48,7 +48,7 @@ def test_workspace_queries_are_pure_host_functions():
     cfg = cake._lib.MoeConfig(4096, 7168, 2048, 256, 256, 8, 8, 4, 1, 0, 0)
     size = cake._lib.workspace_bytes("moe", cfg)
     pairs = 4096 * 8
-    assert size >= pairs * (7168 + 2048 + 7168 * 4) and size < 2 * pairs * (7168 + 2048 + 7168 * 4)
+    assert size >= pairs * (7168 + 2048 + 7168 * 2) and size < 2 * pairs * (7168 + 2048 + 7168 * 2)
     assert cake._lib.workspace_bytes("moe", cake._lib.MoeConfig(4096, 7168 + 1, 2048, 256, 256, 8, 8, 4, 1, 0, 0)) == 0
     g = cake._lib.GqaDecodeConfig(64, 32, 8, 128, 16, 4096)
     assert cake._lib.workspace_bytes("gqa_decode", g) > 64 * 32 * 129 * 4
