@@ -1,16 +1,25 @@
-// Paged MLA decode (absorbed form) for sm_100a: split-KV flash-decode + reduce.
+// Paged MLA decode (absorbed form) for sm_100a: split-KV flash-decode on tcgen05 + reduce.
 //
 // Operator: src/open_cake_ir/tasks/solx_fib/attention.py:132-183, MLA branch (:164-165,
 // :175-177); tensor ABI attention_specs.py:249-292.  All query heads share one latent KV row of
 // 512 (ckv) + 64 (kpe) bf16 per token:  logits = (ckv . q_nope + kpe . q_pe) * scale,
 // out = bf16(softmax(logits) ckv), lse base 2.
 //
-// A CTA owns (64 query heads, sequence, KV chunk) and streams the chunk's latent rows once
-// through a three-stage cp.async ring of 32-token tiles (576 bf16 per row, XOR-swizzled);
-// the two head blocks of a sequence are adjacent CTAs, so the second reads the rows from L2.
-// Eight warps: warp w works on heads 16*(w%4).. and on output dims 256*(w/4)...  Q stays in
-// shared memory for the whole CTA; S = Q K^T and O += P V are m16n8k16 bf16 MMAs fed by
-// ldmatrix, with the online softmax (base 2) in registers between them.
+// At 128 heads the operator does 242 flop per byte of latent cache, which is the bf16 ridge of the
+// machine, so both contractions run on the tensor core.  A CTA owns (128 heads, one half of the 512
+// output dims, sequence, KV chunk); the two halves of a chunk are neighbouring CTAs, so the second
+// reads the latent rows from L2.  The 128 heads are the 128 TMEM lanes:
+//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q and the tile K-major in shared memory
+//   O[128 x 256 dims]  += P[128 x 32] . V[32 x 256]     P from tensor memory, V = the same tile read
+//                                                        MN-major (no transposed copy is made)
+// Q (147 KiB, nine 64-column slabs of 128-byte rows, 128-byte swizzle) stays in shared memory for
+// the whole CTA; 32-token tiles stream through a two-stage cp.async ring in the same slab layout
+// (the gather is per token, so any page size works).  Four softmax warps own one head row each per
+// thread: they read S from TMEM, keep the running max and sum in base 2, and write P back to TMEM
+// as TWO bf16 terms (value + rounding residual; one term is not accurate enough for the
+// contract's tolerance).  The running max only moves when it grows by more than 2^8, so O is
+// rescaled in TMEM rarely.  QK of tile i+1 is issued before PV of tile i, so the tensor core works
+// while the softmax of tile i runs.  Every wait is bounded and reports through the status word.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <new>
@@ -19,16 +28,24 @@ namespace cake {
 namespace mla {
 
 constexpr int kCkv = 512, kKpe = 64, kRow = kCkv + kKpe;   // 576 elements per latent row
-constexpr int kRowBytes = kRow * 2;                        // 1152
-constexpr int kRowChunks = kRowBytes / 16;                 // 72
-constexpr int kHeads = 64;                                 // query heads per CTA
+constexpr int kSlabs = kRow / 64;                          // 9 slabs of 64 columns (128 bytes per row)
+constexpr int kRowChunks = kRow / 8;                       // 72 16-byte chunks per row
+constexpr int kHeads = 128;                                // query heads per CTA = TMEM lanes
+constexpr int kDimsPerCta = 256;                           // output dims per CTA (half of ckv)
 constexpr int kTile = 32;                                  // tokens per tile
-constexpr int kRing = 3;
+constexpr int kStages = 2;
+constexpr int kQSlabBytes = kHeads * 128;                  // 16 KiB
+constexpr int kQBytes = kSlabs * kQSlabBytes;              // 147 456
+constexpr int kKvSlabBytes = kTile * 128;                  // 4 KiB
+constexpr int kKvStageBytes = kSlabs * kKvSlabBytes;       // 36 864
+constexpr int kLoaderWarps = 2, kLoaderThreads = kLoaderWarps * 32;
+constexpr int kMmaWarp = 2;
+constexpr int kSoftmaxWarp0 = 4;                           // warps 4..7: warp % 4 = TMEM lane quadrant
 constexpr int kThreads = 256;
-constexpr int kQBytes = kHeads * kRowBytes;                // 73 728
-constexpr int kTileBytes = kTile * kRowBytes;              // 36 864
-constexpr int kSmemBytes = kQBytes + kRing * kTileBytes;   // 184 320
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;                   // log2 units
+// tensor-memory columns
+constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kTmemColumns = 512;
 
 struct Params {
   const __nv_bfloat16 *q_nope, *q_pe, *ckv, *kpe;
@@ -38,44 +55,41 @@ struct Params {
   float* lse;             // [B, H]
   float* part_o;          // [B, splits, H, 512]
   float* part_lse;        // [B, splits, H]
+  int* status;
   int batch, heads, page_size, chunk, max_splits;
 };
+
+struct Shared {
+  uint64_t kv_full[kStages], kv_empty[kStages];
+  uint64_t s_full[2], s_free[2], p_ready[2], pv_done[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kSmemBytes = size_t(kQBytes) + kStages * kKvStageBytes + sizeof(Shared) + 1024;
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
   return pages <= 0 ? 0 : (pages - 1) * p.page_size + p.kv_last_page_len[b];
 }
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-  const int bytes = valid ? 16 : 0;
+  const int bytes = valid ? 16 : 0;      // 0 source bytes = zero fill
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Byte offset of (row, 16-byte chunk) in a swizzled tile of 1152-byte rows (72 chunks; the XOR
-// stays inside a group of eight chunks).
-__device__ __forceinline__ uint32_t row_off(int row, int chunk) {
-  return uint32_t(row * kRowBytes + ((chunk ^ (row & 7)) << 4));
+
+// Byte offset of 16-byte chunk `chunk` (0..71) of row `row` in a slab-major tile whose slabs hold
+// `rows` rows of 128 bytes with the 128-byte swizzle (chunk index XOR row mod 8).
+__device__ __forceinline__ uint32_t slab_off(int rows, int row, int chunk) {
+  return uint32_t((chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-__device__ __forceinline__ void load_tile(const Params& p, int b, int tok0, int len, uint32_t dst) {
+// One 32-token tile of latent rows -> one ring stage, by the loader threads.
+__device__ __forceinline__ void load_tile(const Params& p, int b, int tok0, int len, uint32_t dst, int loader_tid) {
   const int page_base = p.kv_indptr[b];
-  for (int idx = threadIdx.x; idx < kTile * kRowChunks; idx += kThreads) {
+  for (int idx = loader_tid; idx < kTile * kRowChunks; idx += kLoaderThreads) {
     const int row = idx / kRowChunks, chunk = idx % kRowChunks;
     const int tok = tok0 + row;
     const bool valid = tok < len;
@@ -83,142 +97,213 @@ __device__ __forceinline__ void load_tile(const Params& p, int b, int tok0, int 
     const int page = __ldg(p.kv_indices + page_base + t / p.page_size);
     const size_t slot = size_t(page) * p.page_size + (t % p.page_size);
     const __nv_bfloat16* src = chunk < kCkv / 8 ? p.ckv + slot * kCkv + chunk * 8 : p.kpe + slot * kKpe + (chunk - kCkv / 8) * 8;
-    cp_async_16(dst + row_off(row, chunk), src, valid);
+    cp_async_16(dst + slab_off(kTile, row, chunk), src, valid);
   }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
 mla_decode_kernel(const Params p) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int hb = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  extern __shared__ uint8_t smem_raw[];
+  const int dh = blockIdx.x & 1, hb = blockIdx.x >> 1, split = blockIdx.y, b = blockIdx.z;
   const int len = seq_len(p, b);
   const int begin = split * p.chunk;
   if (begin >= len) return;
   const int end = min(len, begin + p.chunk);
+  const int tiles = (end - begin + kTile - 1) / kTile;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t q_addr = smem_u32(base);
+  const uint32_t kv_addr = q_addr + kQBytes;
+  Shared* sh = reinterpret_cast<Shared*>(base + kQBytes + kStages * kKvStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hg = warp & 3, dh = warp >> 2;
-  const int row = lane >> 2, quad = lane & 3;
-  const float scale2 = __ldg(p.sm_scale) * kLog2e;
-  const uint32_t q_smem = smem_u32(smem);
-  const uint32_t ring = q_smem + kQBytes;
   const int head0 = hb * kHeads;
 
-  // Q block -> shared memory (rows beyond the head count are zero-filled)
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&sh->kv_full[s], kLoaderThreads); mbar_init(&sh->kv_empty[s], 1); }
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(&sh->s_full[j], 1); mbar_init(&sh->s_free[j], 4);
+      mbar_init(&sh->p_ready[j], 4); mbar_init(&sh->pv_done[j], 1);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(&sh->tmem_base, kTmemColumns);
+    tmem_relinquish();
+  }
+  // Q block -> shared memory, slab-major and swizzled like a TMA box would leave it
   for (int idx = threadIdx.x; idx < kHeads * kRowChunks; idx += kThreads) {
     const int r = idx / kRowChunks, chunk = idx % kRowChunks;
     const int head = head0 + r;
     const bool valid = head < p.heads;
     const size_t hrow = size_t(b) * p.heads + (valid ? head : 0);
     const __nv_bfloat16* src = chunk < kCkv / 8 ? p.q_nope + hrow * kCkv + chunk * 8 : p.q_pe + hrow * kKpe + (chunk - kCkv / 8) * 8;
-    cp_async_16(q_smem + row_off(r, chunk), src, valid);
+    cp_async_16(q_addr + slab_off(kHeads, r, chunk), src, valid);
   }
-  const int tiles = (end - begin + kTile - 1) / kTile;
-#pragma unroll
-  for (int s = 0; s < kRing - 1; ++s) {
-    if (s < tiles) load_tile(p, b, begin + s * kTile, end, ring + s * kTileBytes);
-    cp_async_commit();      // the first group also carries Q
-  }
-
-  float o[32][4];
-#pragma unroll
-  for (int n = 0; n < 32; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows `row` and `row + 8` of this warp's 16 heads
-  const int mi = lane >> 3, lr = lane & 7;
-
-  for (int i = 0; i < tiles; ++i) {
-    cp_async_wait<kRing - 2>();
-    __syncthreads();                 // tile i visible to all; everyone is done with tile i-1
-    {
-      const int next = i + kRing - 1;
-      if (next < tiles) load_tile(p, b, begin + next * kTile, end, ring + (next % kRing) * kTileBytes);
-      cp_async_commit();
-    }
-    const uint32_t kv = ring + (i % kRing) * kTileBytes;
-    const int tok0 = begin + i * kTile;
-
-    // S[16 heads x 32 tokens] over the 576-wide latent row
-    float s[4][4];
-#pragma unroll
-    for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
-#pragma unroll 4
-    for (int ks = 0; ks < kRow / 16; ++ks) {
-      uint32_t a0, a1, a2, a3;
-      // A: matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15) of this warp's 16 heads
-      ldmatrix_x4(q_smem + row_off(hg * 16 + (mi & 1) * 8 + lr, ks * 2 + (mi >> 1)), a0, a1, a2, a3);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(kv + row_off(half * 16 + (mi >> 1) * 8 + lr, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-        mma_bf16_16816(s[half * 2], a0, a1, a2, a3, b0, b1);
-        mma_bf16_16816(s[half * 2 + 1], a0, a1, a2, a3, b2, b3);
-      }
-    }
-    // online softmax; lane holds tokens tok0 + n*8 + quad*2 + {0,1} of rows `row` (c0,c1) and `row+8` (c2,c3)
-    float tmax0 = -INFINITY, tmax1 = -INFINITY;
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const bool valid = tok0 + n * 8 + quad * 2 + j < end;
-        s[n][j] = valid ? s[n][j] * scale2 : -INFINITY;
-        s[n][2 + j] = valid ? s[n][2 + j] * scale2 : -INFINITY;
-        tmax0 = fmaxf(tmax0, s[n][j]);
-        tmax1 = fmaxf(tmax1, s[n][2 + j]);
-      }
-    }
-    tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
-    tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
-    tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
-    tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
-    const float n0 = fmaxf(m0, tmax0), n1 = fmaxf(m1, tmax1);
-    const float alpha0 = exp2f(m0 - n0), alpha1 = exp2f(m1 - n1);
-    m0 = n0; m1 = n1;
-    float sum0 = 0.f, sum1 = 0.f;
-    uint32_t pa[4][2], pb[4][2];   // P as bf16 pairs, value and rounding residual: [n-tile][row | row+8]
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const float p0 = exp2f(s[n][0] - n0), p1 = exp2f(s[n][1] - n0);
-      const float p2 = exp2f(s[n][2] - n1), p3 = exp2f(s[n][3] - n1);
-      sum0 += p0 + p1; sum1 += p2 + p3;
-      split_bf16x2(p0, p1, pa[n][0], pb[n][0]);
-      split_bf16x2(p2, p3, pa[n][1], pb[n][1]);
-    }
-    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-    l0 = l0 * alpha0 + sum0;
-    l1 = l1 * alpha1 + sum1;
-#pragma unroll
-    for (int n = 0; n < 32; ++n) { o[n][0] *= alpha0; o[n][1] *= alpha0; o[n][2] *= alpha1; o[n][3] *= alpha1; }
-    // O[16 heads x 256 dims] += P[16 x 32] V[32 x 256]; V = the ckv part of the same tile
-#pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-#pragma unroll
-      for (int np = 0; np < 16; ++np) {
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4_trans(kv + row_off(ks * 16 + (mi & 1) * 8 + lr, dh * 32 + np * 2 + (mi >> 1)), b0, b1, b2, b3);
-        mma_bf16_16816(o[np * 2], pa[ks * 2][0], pa[ks * 2][1], pa[ks * 2 + 1][0], pa[ks * 2 + 1][1], b0, b1);
-        mma_bf16_16816(o[np * 2], pb[ks * 2][0], pb[ks * 2][1], pb[ks * 2 + 1][0], pb[ks * 2 + 1][1], b0, b1);
-        mma_bf16_16816(o[np * 2 + 1], pa[ks * 2][0], pa[ks * 2][1], pa[ks * 2 + 1][0], pa[ks * 2 + 1][1], b2, b3);
-        mma_bf16_16816(o[np * 2 + 1], pb[ks * 2][0], pb[ks * 2][1], pb[ks * 2 + 1][0], pb[ks * 2 + 1][1], b2, b3);
-      }
-    }
-  }
+  cp_async_commit();
   cp_async_wait<0>();
+  fence_proxy_async_smem();
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
 
-  // partial results: normalised output and base-2 log-sum-exp of this chunk
-  const float inv0 = 1.f / l0, inv1 = 1.f / l1;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int head = head0 + hg * 16 + row + half * 8;
-    if (head < p.heads) {
-      const size_t slot = (size_t(b) * p.max_splits + split) * p.heads + head;
-      float* dst = p.part_o + slot * kCkv + dh * 256 + quad * 2;
-      const float inv = half ? inv1 : inv0;
-#pragma unroll
-      for (int n = 0; n < 32; ++n)
-        *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
-      if (dh == 0 && quad == 0) p.part_lse[slot] = (half ? m1 : m0) + log2f(half ? l1 : l0);
+  if (warp < kLoaderWarps) {
+    // ------------------------------ loader --------------------------------------------
+    bool ok = true;
+    for (int i = 0; ok && i < tiles; ++i) {
+      const int s = i % kStages;
+      ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
+      if (!ok) break;
+      load_tile(p, b, begin + i * kTile, end, kv_addr + s * kKvStageBytes, threadIdx.x);
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      mbar_arrive(&sh->kv_full[s]);
     }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------ MMA issuer ----------------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_qk = umma_idesc_ex(1 /* bf16 */, kHeads, kTile, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_ex(1 /* bf16 */, kHeads, kDimsPerCta, 0, 1 /* V is MN-major */);
+      bool ok = true;
+      for (int i = 0; ok && i <= tiles; ++i) {
+        if (i < tiles) {          // S(i) = Q . tile(i)^T
+          const int s = i % kStages, j = i & 1;
+          ok = mbar_wait(&sh->kv_full[s], (i / kStages) & 1, abort_flag, p.status, kStatusWaitSmemFull) &&
+               mbar_wait(&sh->s_free[j], ((i >> 1) & 1) ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t tile_addr = kv_addr + s * kKvStageBytes;
+#pragma unroll 1
+          for (int slab = 0; slab < kSlabs; ++slab) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t a_desc = umma_desc_sw128(q_addr + slab * kQSlabBytes + kk * 32);
+              const uint64_t b_desc = umma_desc_sw128(tile_addr + slab * kKvSlabBytes + kk * 32);
+              umma_f16(tmem_base + kColS + j * kTile, a_desc, b_desc, idesc_qk, (slab | kk) != 0);
+            }
+          }
+          tcgen05_commit(&sh->s_full[j]);
+        }
+        if (i >= 1) {             // O += P(i-1) . V(i-1), P as two bf16 terms
+          const int t = i - 1, s = t % kStages, j = t & 1;
+          ok = mbar_wait(&sh->p_ready[j], (t >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t v_addr = kv_addr + s * kKvStageBytes + dh * (kDimsPerCta / 64) * kKvSlabBytes;
+#pragma unroll
+          for (int term = 0; term < 2; ++term) {
+#pragma unroll
+            for (int ks = 0; ks < kTile / 16; ++ks) {
+              const uint32_t a_tmem = tmem_base + kColP + j * kTile + term * (kTile / 2) + ks * 8;
+              // 16 tokens = two 8-row groups of 1024 bytes; the next 64 dims are one slab further
+              const uint64_t b_desc = umma_desc_sw128_ex(v_addr + ks * 2048, kKvSlabBytes, 1024);
+              umma_f16_a_tmem(tmem_base + kColO, a_tmem, b_desc, idesc_pv, (t | term | ks) != 0);
+            }
+          }
+          tcgen05_commit(&sh->pv_done[j]);
+          tcgen05_commit(&sh->kv_empty[s]);
+        }
+      }
+    }
+  } else if (warp >= kSoftmaxWarp0) {
+    // ------------------------------ softmax / epilogue --------------------------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;                 // head row of this thread
+    const uint32_t lane_base = tmem_base + (uint32_t(quad * 32) << 16);
+    const float scale2 = __ldg(p.sm_scale) * kLog2e;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; ok && i < tiles; ++i) {
+      const int j = i & 1;
+      ok = mbar_wait(&sh->s_full[j], (i >> 1) & 1, abort_flag, p.status, kStatusWaitTmemFull);
+      if (!ok) break;
+      tcgen05_fence_after();
+      float sc[kTile];
+      tmem_ld_32x32b_x32(lane_base + kColS + j * kTile, sc);
+      tcgen05_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->s_free[j]);
+      const int tok0 = begin + i * kTile;
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < kTile; ++c) {
+        sc[c] = tok0 + c < end ? sc[c] * scale2 : -INFINITY;
+        tmax = fmaxf(tmax, sc[c]);
+      }
+      if (i == 0) {
+        m_ref = tmax;                                // finite: the first tile holds a valid token
+      } else {
+        const bool need = tmax > m_ref + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          // O is about to be rescaled in tensor memory: the PV of the previous tile must have landed
+          ok = mbar_wait(&sh->pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
+          if (need) { m_ref = tmax; l *= alpha; }
+#pragma unroll 1
+          for (int c = 0; c < kDimsPerCta; c += 32) {
+            float o[32];
+            tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+            tcgen05_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] *= alpha;
+            tmem_st_32x32b_x32(lane_base + kColO + c, o);
+          }
+          tcgen05_wait_st();
+        }
+      }
+      if (i >= 2) {              // the P buffer is free once the PV that read it has completed
+        ok = mbar_wait(&sh->pv_done[j], ((i - 2) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+        if (!ok) break;
+      }
+      uint32_t hi[kTile / 2], lo[kTile / 2];
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < kTile; c += 2) {
+        const float p0 = exp2f(sc[c] - m_ref), p1 = exp2f(sc[c + 1] - m_ref);
+        sum += p0 + p1;
+        split_bf16x2(p0, p1, hi[c >> 1], lo[c >> 1]);
+      }
+      l += sum;
+      tmem_st_32x32b_x16(lane_base + kColP + j * kTile, hi);
+      tmem_st_32x32b_x16(lane_base + kColP + j * kTile + kTile / 2, lo);
+      tcgen05_wait_st();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->p_ready[j]);
+    }
+    if (ok) ok = mbar_wait(&sh->pv_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+    if (ok) {
+      tcgen05_fence_after();
+      const int head = head0 + r;
+      const float inv = 1.f / l;
+      const size_t slot = (size_t(b) * p.max_splits + split) * p.heads + (head < p.heads ? head : 0);
+      float* dst = p.part_o + slot * kCkv + dh * kDimsPerCta;
+#pragma unroll 1
+      for (int c = 0; c < kDimsPerCta; c += 32) {
+        float o[32];
+        tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+        tcgen05_wait_ld();
+        if (head < p.heads) {
+#pragma unroll
+          for (int k = 0; k < 32; k += 4)
+            *reinterpret_cast<float4*>(dst + c + k) = make_float4(o[k] * inv, o[k + 1] * inv, o[k + 2] * inv, o[k + 3] * inv);
+        }
+      }
+      if (dh == 0 && head < p.heads) p.part_lse[slot] = m_ref + log2f(l);
+    }
+  }
+
+  cp_async_wait<0>();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemColumns);
   }
 }
 
@@ -259,10 +344,10 @@ struct Handle {
 inline int pick_chunk(const cake_b200_mla_decode_config& c, int sms) {
   // Few, long chunks keep the partial-output traffic (heads * 512 fp32 per chunk) small next to
   // the latent rows a chunk reads (1152 B per token); enough of them to fill the SMs.
-  const long long head_blocks = (c.num_qo_heads + kHeads - 1) / kHeads;
+  const long long head_blocks = 2LL * ((c.num_qo_heads + kHeads - 1) / kHeads);     // two dim halves per 128 heads
   const long long max_len = c.max_kv_len > 0 ? c.max_kv_len : 1;
   int chunk = 4096;
-  while (chunk > 128 && c.batch * head_blocks * ((max_len * 5 / 8 + chunk - 1) / chunk) < 2LL * sms) chunk >>= 1;
+  while (chunk > 128 && c.batch * head_blocks * ((max_len * 5 / 8 + chunk - 1) / chunk) < 3LL * sms) chunk >>= 1;
   return chunk;
 }
 
@@ -312,10 +397,11 @@ extern "C" int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_d
   p.page_size = config->page_size;
   p.chunk = mla::pick_chunk(*config, 148);
   p.max_splits = int((config->max_kv_len + p.chunk - 1) / p.chunk) + 1;
+  p.status = static_cast<int*>(buffers[10]);
   uint8_t* ws = static_cast<uint8_t*>(buffers[10]) + 256;
   p.part_o = reinterpret_cast<float*>(ws);
   p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.heads * mla::kCkv;
-  int rc = int(cudaFuncSetAttribute(mla::mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla::kSmemBytes));
+  int rc = int(cudaFuncSetAttribute(mla::mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(mla::kSmemBytes)));
   if (rc) { delete h; return rc; }
   *handle_out = h;
   return 0;
@@ -331,8 +417,9 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   const mla::Params& p = h->p;
   if (p.batch == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  CAKE_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), s));
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
-  mla::mla_decode_kernel<<<dim3(head_blocks, p.max_splits, p.batch), mla::kThreads, mla::kSmemBytes, s>>>(p);
+  mla::mla_decode_kernel<<<dim3(2 * head_blocks, p.max_splits, p.batch), mla::kThreads, mla::kSmemBytes, s>>>(p);
   mla::mla_reduce_kernel<<<dim3(p.heads, p.batch), 128, 0, s>>>(p);
   return int(cudaGetLastError());
 }
