@@ -13,13 +13,13 @@
 //   O[128 x 256 dims]  += P[128 x 32] . V[32 x 256]     P from tensor memory, V = the same tile read
 //                                                        MN-major (no transposed copy is made)
 // Q (147 KiB, nine 64-column slabs of 128-byte rows, 128-byte swizzle) stays in shared memory for
-// the whole CTA; 32-token tiles stream through a two-stage cp.async ring in the same slab layout
+// the whole CTA (its size is what limits the ring to two stages); 32-token tiles stream through a
+// two-stage cp.async ring in the same slab layout
 // (the gather is per token, so any page size works).  Four softmax warps own one head row each per
 // thread: they read S from TMEM, keep the running max and sum in base 2, and write P back to TMEM
 // as TWO bf16 terms (value + rounding residual; one term is not accurate enough for the
 // contract's tolerance).  The running max only moves when it grows by more than 2^8, so O is
-// rescaled in TMEM rarely.  QK of tile i+1 is issued before PV of tile i, so the tensor core works
-// while the softmax of tile i runs.  Every wait is bounded and reports through the status word.
+// rescaled in TMEM rarely.  Every wait is bounded and reports through the status word.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <new>
@@ -86,18 +86,25 @@ __device__ __forceinline__ uint32_t slab_off(int rows, int row, int chunk) {
   return uint32_t((chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// One 32-token tile of latent rows -> one ring stage, by the loader threads.
+// One 32-token tile of latent rows -> one ring stage, by the two loader warps.  A warp takes 16
+// rows; its lanes cover consecutive 16-byte chunks of one row at a time (coalesced 512-byte reads),
+// and the page of each row is looked up once per tile by one lane and passed round by shuffle.
 __device__ __forceinline__ void load_tile(const Params& p, int b, int tok0, int len, uint32_t dst, int loader_tid) {
-  const int page_base = p.kv_indptr[b];
-  for (int idx = loader_tid; idx < kTile * kRowChunks; idx += kLoaderThreads) {
-    const int row = idx / kRowChunks, chunk = idx % kRowChunks;
-    const int tok = tok0 + row;
-    const bool valid = tok < len;
-    const int t = valid ? tok : 0;
-    const int page = __ldg(p.kv_indices + page_base + t / p.page_size);
-    const size_t slot = size_t(page) * p.page_size + (t % p.page_size);
-    const __nv_bfloat16* src = chunk < kCkv / 8 ? p.ckv + slot * kCkv + chunk * 8 : p.kpe + slot * kKpe + (chunk - kCkv / 8) * 8;
-    cp_async_16(dst + slab_off(kTile, row, chunk), src, valid);
+  const int w = loader_tid >> 5, lane = loader_tid & 31;
+  const int my_tok = tok0 + w * 16 + (lane & 15);
+  const bool my_valid = my_tok < len;
+  const int t = my_valid ? my_tok : 0;
+  const int page = __ldg(p.kv_indices + p.kv_indptr[b] + t / p.page_size);
+  const long long my_slot = (long long)page * p.page_size + (t % p.page_size);
+#pragma unroll
+  for (int rr = 0; rr < 16; ++rr) {
+    const int row = w * 16 + rr;
+    const long long slot = __shfl_sync(0xffffffffu, my_slot, rr);
+    const bool valid = __shfl_sync(0xffffffffu, int(my_valid), rr) != 0;
+    const __nv_bfloat16* ckv_row = p.ckv + slot * kCkv;
+    cp_async_16(dst + slab_off(kTile, row, lane), ckv_row + lane * 8, valid);
+    cp_async_16(dst + slab_off(kTile, row, 32 + lane), ckv_row + (32 + lane) * 8, valid);
+    if (lane < kKpe / 8) cp_async_16(dst + slab_off(kTile, row, kCkv / 8 + lane), p.kpe + slot * kKpe + lane * 8, valid);
   }
 }
 
@@ -130,6 +137,8 @@ mla_decode_kernel(const Params p) {
     tmem_alloc(&sh->tmem_base, kTmemColumns);
     tmem_relinquish();
   }
+  // the loader warps start the first tile before anything else so that it travels with the Q block
+  if (warp < kLoaderWarps) load_tile(p, b, begin, end, kv_addr, threadIdx.x);
   // Q block -> shared memory, slab-major and swizzled like a TMA box would leave it
   for (int idx = threadIdx.x; idx < kHeads * kRowChunks; idx += kThreads) {
     const int r = idx / kRowChunks, chunk = idx % kRowChunks;
@@ -155,9 +164,11 @@ mla_decode_kernel(const Params p) {
       const int s = i % kStages;
       ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
       if (!ok) break;
-      load_tile(p, b, begin + i * kTile, end, kv_addr + s * kKvStageBytes, threadIdx.x);
-      cp_async_commit();
-      cp_async_wait<0>();
+      if (i > 0) {               // tile 0 was issued, and has landed, with the Q block
+        load_tile(p, b, begin + i * kTile, end, kv_addr + s * kKvStageBytes, threadIdx.x);
+        cp_async_commit();
+        cp_async_wait<0>();
+      }
       fence_proxy_async_smem();
       mbar_arrive(&sh->kv_full[s]);
     }
@@ -168,24 +179,8 @@ mla_decode_kernel(const Params p) {
       constexpr uint32_t idesc_pv = umma_idesc_ex(1 /* bf16 */, kHeads, kDimsPerCta, 0, 1 /* V is MN-major */);
       bool ok = true;
       for (int i = 0; ok && i <= tiles; ++i) {
-        if (i < tiles) {          // S(i) = Q . tile(i)^T
-          const int s = i % kStages, j = i & 1;
-          ok = mbar_wait(&sh->kv_full[s], (i / kStages) & 1, abort_flag, p.status, kStatusWaitSmemFull) &&
-               mbar_wait(&sh->s_free[j], ((i >> 1) & 1) ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty);
-          if (!ok) break;
-          tcgen05_fence_after();
-          const uint32_t tile_addr = kv_addr + s * kKvStageBytes;
-#pragma unroll 1
-          for (int slab = 0; slab < kSlabs; ++slab) {
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t a_desc = umma_desc_sw128(q_addr + slab * kQSlabBytes + kk * 32);
-              const uint64_t b_desc = umma_desc_sw128(tile_addr + slab * kKvSlabBytes + kk * 32);
-              umma_f16(tmem_base + kColS + j * kTile, a_desc, b_desc, idesc_qk, (slab | kk) != 0);
-            }
-          }
-          tcgen05_commit(&sh->s_full[j]);
-        }
+        // PV of the previous tile goes first: it is what releases that tile's ring stage, and with
+        // two stages the loader needs it back before it can fetch tile i+1.
         if (i >= 1) {             // O += P(i-1) . V(i-1), P as two bf16 terms
           const int t = i - 1, s = t % kStages, j = t & 1;
           ok = mbar_wait(&sh->p_ready[j], (t >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
@@ -204,6 +199,24 @@ mla_decode_kernel(const Params p) {
           }
           tcgen05_commit(&sh->pv_done[j]);
           tcgen05_commit(&sh->kv_empty[s]);
+        }
+        if (i < tiles) {          // S(i) = Q . tile(i)^T
+          const int s = i % kStages, j = i & 1;
+          ok = mbar_wait(&sh->kv_full[s], (i / kStages) & 1, abort_flag, p.status, kStatusWaitSmemFull) &&
+               mbar_wait(&sh->s_free[j], ((i >> 1) & 1) ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t tile_addr = kv_addr + s * kKvStageBytes;
+#pragma unroll 1
+          for (int slab = 0; slab < kSlabs; ++slab) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t a_desc = umma_desc_sw128(q_addr + slab * kQSlabBytes + kk * 32);
+              const uint64_t b_desc = umma_desc_sw128(tile_addr + slab * kKvSlabBytes + kk * 32);
+              umma_f16(tmem_base + kColS + j * kTile, a_desc, b_desc, idesc_qk, (slab | kk) != 0);
+            }
+          }
+          tcgen05_commit(&sh->s_full[j]);
         }
       }
     }
