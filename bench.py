@@ -63,7 +63,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=self.file,
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -81,20 +81,24 @@ class ClockSampler:
         self.file.flush()
         rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 8]
         os.unlink(self.file.name)
-        sm = []
+        sm, power = [], []
         reasons = set()
         max_mhz = None
         for r in rows:
             try:
-                sm.append(float(r[1])); max_mhz = float(r[2])
+                clock, watts = float(r[1]), float(r[3])
+                max_mhz = float(r[2])
             except ValueError:
                 continue
+            sm.append(clock); power.append(watts)
             for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
                 if cell.strip().lower().startswith("active"):
                     reasons.add(name)
-        busy = [v for v in sm if max_mhz and v > 0.5 * max_mhz] or sm
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max_mhz, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        # "under load" = samples drawing at least half of the highest power seen during the region
+        top = max(power) if power else 0.0
+        loaded = [c for c, w in zip(sm, power) if w >= 0.5 * top] or sm
+        return {"sm_mhz": statistics.median(loaded) if loaded else None, "sm_max_mhz": max_mhz, "reasons": sorted(reasons),
+                "samples": len(sm), "samples_under_load": len(loaded), "power_w_max": top}
 
 
 def dist_setup(n_gpus: int):
@@ -166,6 +170,52 @@ def time_cold(launch, iters: int, warmup: int) -> float:
     return statistics.mean(times)
 
 
+E2E_INPUTS = ("routing_logits", "hidden_states", "hidden_states_scale")
+
+
+def pipelined_e2e(make_set, dev, out):
+    """Builds the end-to-end step: host inputs -> device, layer, output -> host, with the copies of
+    neighbouring steps overlapping this step's kernels.  ``make_set()`` returns (device inputs, device
+    output, launch(stream)) for one of the two buffer sets.  Returns (step, h2d bytes, d2h bytes)."""
+    host_in = {k: dev[k].cpu().pin_memory() for k in E2E_INPUTS}
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = out.numel() * out.element_size()
+    sets = []
+    for _ in range(2):
+        inputs, o, launch = make_set()
+        sets.append({"in": inputs, "out": o, "launch": launch, "host_out": torch.empty_like(out, device="cpu").pin_memory(),
+                     "h2d_done": torch.cuda.Event(), "compute_done": torch.cuda.Event(), "d2h_done": torch.cuda.Event()})
+    copy_in, compute, copy_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    counter = {"k": 0}
+
+    def step():
+        k = counter["k"]; counter["k"] += 1
+        b = sets[k & 1]
+        if k == 0:
+            for st in (copy_in, compute, copy_out):
+                st.wait_stream(main)
+        with torch.cuda.stream(copy_in):
+            if k >= 2:
+                copy_in.wait_event(b["compute_done"])        # step k-2 has consumed these inputs
+            for name in E2E_INPUTS:
+                b["in"][name].copy_(host_in[name], non_blocking=True)
+            b["h2d_done"].record(copy_in)
+        with torch.cuda.stream(compute):
+            compute.wait_event(b["h2d_done"])
+            if k >= 2:
+                compute.wait_event(b["d2h_done"])            # step k-2's output has left the device
+            b["launch"](compute)
+            b["compute_done"].record(compute)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(b["compute_done"])
+            b["host_out"].copy_(b["out"], non_blocking=True)
+            b["d2h_done"].record(copy_out)
+        main.wait_stream(copy_out)                           # the timing events live on the main stream
+
+    return step, h2d, d2h
+
+
 # ------------------------------------------------------------------------------------------------
 def moe_single(steps, warmup, peaks):
     import open_cake_ir_b200 as cake
@@ -175,8 +225,9 @@ def moe_single(steps, warmup, peaks):
     out = torch.empty((SHAPE["tokens"], SHAPE["hidden"]), dtype=torch.bfloat16, device="cuda")
     op = cake.Fp8Moe(dev, out, routing="softmax", act_mode="fp8")
     flops = cake.workloads.moe_flops(SHAPE["tokens"], SHAPE["hidden"], SHAPE["inter"])
-    with ClockSampler(torch.cuda.current_device()) as clocks:
-        ms = time_steps(op.launch, steps, warmup, 1)
+    clocks = ClockSampler(torch.cuda.current_device())
+    clocks.__enter__()                     # sampled until the end-to-end loop below has finished
+    ms = time_steps(op.launch, steps, warmup, 1)
     if op.status():
         raise RuntimeError("a device-side wait ran out")
     # stage timing (inputs 11 GB >> L2, so consecutive launches are cold anyway)
@@ -198,19 +249,19 @@ def moe_single(steps, warmup, peaks):
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_source": peaks["source"], "algorithmic_bytes": gemm1_bytes, "ms": stage_ms[1], "traffic": None,
                 "tflops": 2 * pairs * 2 * SHAPE["inter"] * SHAPE["hidden"] / (stage_ms[1] * 1e-3) / 1e12}
-    # end to end with host buffers
-    host_in = {k: dev[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
-    host_out = torch.empty_like(out, device="cpu").pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
-    d2h = out.numel() * out.element_size()
+    # End to end with host buffers: steps are independent layers over fresh activations, so the copies of
+    # neighbouring steps overlap this step's kernels (two buffer sets over the same resident weights).
+    def make_set():
+        inputs = dict(dev)
+        for k in E2E_INPUTS:
+            inputs[k] = torch.empty_like(dev[k])
+        o = torch.empty_like(out)
+        layer = cake.Fp8Moe(inputs, o, routing="softmax", act_mode="fp8")
+        return inputs, o, layer.launch
 
-    def e2e_step():
-        for k, t in host_in.items():
-            dev[k].copy_(t, non_blocking=True)
-        op.launch()
-        host_out.copy_(out, non_blocking=True)
-
+    e2e_step, h2d, d2h = pipelined_e2e(make_set, dev, out)
     e2e_ms = time_steps(e2e_step, steps, warmup, 1)
+    clocks.__exit__()
     return {"ms": ms, "flops": flops, "clocks": clocks.summary(), "stage_ms": dict(zip(cake.Fp8Moe.STAGES, stage_ms)),
             "roofline": roofline, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h, "launches": 8 * steps}
 
@@ -230,20 +281,25 @@ def moe_parallel(steps, warmup, world, rank):
     def step():
         result["out"] = layer.forward()
 
-    with ClockSampler(torch.cuda.current_device()) as clocks:
-        ms = time_steps(step, steps, warmup, world)
-    host_in = {k: dev[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")}
-    host_out = torch.empty((t_local, SHAPE["hidden"]), dtype=torch.bfloat16).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
-    d2h = host_out.numel() * 2
+    clocks = ClockSampler(torch.cuda.current_device())
+    clocks.__enter__()
+    ms = time_steps(step, steps, warmup, world)
+    def make_set():
+        inputs = dict(dev)
+        for k in E2E_INPUTS:
+            inputs[k] = torch.empty_like(dev[k])
+        twin = ep.NativeExpertParallelMoe(inputs, inputs["routing_logits"], inputs["routing_bias"], inputs["hidden_states"],
+                                          inputs["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"],
+                                          routing="softmax")
 
-    def e2e_step():
-        for k, t in host_in.items():
-            dev[k].copy_(t, non_blocking=True)
-        step()
-        host_out.copy_(result["out"], non_blocking=True)
+        def launch(stream):
+            with torch.cuda.stream(stream):
+                twin.forward()
+        return inputs, twin.output, launch
 
+    e2e_step, h2d, d2h = pipelined_e2e(make_set, dev, layer.output)
     e2e_ms = time_steps(e2e_step, steps, warmup, world)
+    clocks.__exit__()
     flops = cake.workloads.moe_flops(SHAPE["tokens"], SHAPE["hidden"], SHAPE["inter"])
     return {"ms": ms, "flops": flops, "clocks": clocks.summary(), "e2e_ms": e2e_ms, "h2d": h2d * world, "d2h": d2h * world,
             "launches": layer.launches_per_step * steps,
@@ -341,12 +397,13 @@ def profile_case(name: str, launches: int = 3):
 
 
 # ------------------------------------------------------------------------------------------------
-CPU_SAMPLE = dict(tokens=2048, local_experts=32, local_offset=0)
+CPU_SAMPLE = dict(tokens=4096, local_experts=96, local_offset=0)
 
 
 def cpu_reference_step(state):
-    """One bounded sample of the workload on the host: 256 tokens routed over all 256 experts, the
-    contributions of the first 8 experts computed by the oracle in fp32 on all host threads."""
+    """One bounded sample of the workload on the host: CPU_SAMPLE["tokens"] tokens routed over all 256
+    experts, the contributions of the first CPU_SAMPLE["local_experts"] experts computed by the oracle in
+    fp32 on all host threads (an expert-parallel rank's share of the layer)."""
     from oracle import moe as oracle_moe
     t0 = time.perf_counter()
     result = oracle_moe.moe_reference(state["inputs"], routing="softmax", act_quant="fp8", dtype=torch.float32, return_parts=True)
