@@ -281,6 +281,9 @@ def moe_parallel(steps, warmup, world, rank):
     def step():
         result["out"] = layer.forward()
 
+    step()
+    if os.environ.get("CAKE_BENCH_NO_GRAPH") != "1":
+        layer.capture()                    # one CUDA graph per step: kernels + both all-to-alls
     clocks = ClockSampler(torch.cuda.current_device())
     clocks.__enter__()
     ms = time_steps(step, steps, warmup, world)
@@ -291,6 +294,10 @@ def moe_parallel(steps, warmup, world, rank):
         twin = ep.NativeExpertParallelMoe(inputs, inputs["routing_logits"], inputs["routing_bias"], inputs["hidden_states"],
                                           inputs["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"],
                                           routing="softmax")
+
+        twin.forward()
+        if os.environ.get("CAKE_BENCH_NO_GRAPH") != "1":
+            twin.capture()
 
         def launch(stream):
             with torch.cuda.stream(stream):

@@ -218,7 +218,28 @@ class NativeExpertParallelMoe:
         if code:
             raise self._lib.CakeError("cake_b200_ep_exchange_launch_stage", code)
 
+    def capture(self) -> None:
+        """Records one step (kernels and both all-to-alls) into a CUDA graph on a side stream; later
+        ``forward()`` calls replay it, which removes the per-launch host cost that dominates once a rank's
+        share of the layer is a few hundred microseconds.  Call after at least one eager step."""
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            self._eager()                       # settle lazy initialisation on this stream
+            stream.synchronize()
+            with torch.cuda.graph(graph, stream=stream):
+                self._eager()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self._graph = graph
+
     def forward(self) -> torch.Tensor:
+        if getattr(self, "_graph", None) is not None:
+            self._graph.replay()
+            return self.output
+        return self._eager()
+
+    def _eager(self) -> torch.Tensor:
         with torch.cuda.device(self.device):
             self.router.launch()
             self._stage(0)
