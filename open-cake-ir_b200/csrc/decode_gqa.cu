@@ -265,6 +265,7 @@ gqa_reduce_kernel(const Params p) {
 struct Handle {
   int device;
   Params p;
+  int* status;      // first word of the workspace; this operator has no device-side waits, it stays 0
 };
 
 inline int pick_chunk(const cake_b200_gqa_decode_config& c, int sms) {
@@ -324,6 +325,7 @@ extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_d
   p.page_size = config->page_size;
   p.chunk = gqa::pick_chunk(*config, 148);
   p.max_splits = int((config->max_kv_len + p.chunk - 1) / p.chunk) + 1;
+  h->status = static_cast<int*>(buffers[9]);
   uint8_t* ws = static_cast<uint8_t*>(buffers[9]) + 256;
   p.part_o = reinterpret_cast<float*>(ws);
   p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.hq * gqa::kD;
@@ -343,6 +345,7 @@ extern "C" int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream) {
   const gqa::Params& p = h->p;
   if (p.batch == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  CAKE_CUDA_OK(cudaMemsetAsync(h->status, 0, sizeof(int), s));
   gqa::gqa_decode_kernel<<<dim3(p.max_splits, p.hkv, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
   gqa::gqa_reduce_kernel<<<dim3(p.hq, p.batch), gqa::kD, 0, s>>>(p);
   return int(cudaGetLastError());
