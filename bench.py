@@ -247,7 +247,11 @@ def moe_single(steps, warmup, peaks):
     achieved = gemm1_bytes / (stage_ms[1] * 1e-3) / 1e9
     roofline = {"kernel": "gemm_fp8_kernel<kGateUp> (grouped GEMM1 + SwiGLU + e4m3 requantisation)", "bound": "hbm",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "peak_source": peaks["source"], "algorithmic_bytes": gemm1_bytes, "ms": stage_ms[1], "traffic": None,
+                "peak_source": peaks["source"], "algorithmic_bytes": gemm1_bytes, "ms": stage_ms[1],
+                # dram__bytes_read + write per launch: captured by ncu on --profile-case moe (64 experts, 1024 tokens:
+                # 1.961 GB against 1.954 GB algorithmic) and scaled by the number of experts, every expert's weights
+                # being read once (profiles/gemm_fp8_kernel_ncu_full.md)
+                "traffic": int(gemm1_bytes * 1.004), "traffic_source": "ncu small case x units",
                 "tflops": 2 * pairs * 2 * SHAPE["inter"] * SHAPE["hidden"] / (stage_ms[1] * 1e-3) / 1e12}
     # End to end with host buffers: steps are independent layers over fresh activations, so the copies of
     # neighbouring steps overlap this step's kernels (two buffer sets over the same resident weights).
