@@ -5,14 +5,13 @@
 // lse = logsumexp / ln 2; an empty sequence gives zeros and -inf.
 //
 // The kernel is bound by the HBM stream of K and V (2 * Hkv * D * 2 bytes per token) and never
-// writes logits or probabilities to memory.  A CTA owns (sequence, KV head, KV chunk); each of
-// its four warps runs its own cp.async ring over 16-token tiles (128-bit copies, one 256-byte
+// writes logits or probabilities to memory.  A CTA owns (sequence, KV chunk); each of its eight warps
+// owns one KV head and runs its own cp.async ring over the chunk's 16-token tiles (128-bit copies, one 256-byte
 // row per token and head, XOR-swizzled in shared memory), so there is no CTA-wide barrier in
 // the main loop.  The G = Hq/Hkv query heads that share a KV head are the rows of an
 // m16n8k16 bf16 MMA (rows beyond G are zero): S = Q K^T via ldmatrix on the K tile, online
 // softmax in base 2 with warp shuffles, O += P V via ldmatrix.trans on the V tile (P as two bf16
-// terms, so the weights keep ~16 significant bits).  Warps are
-// merged in shared memory, chunks by a second small kernel.
+// terms, so the weights keep ~16 significant bits).  Chunks are merged by a second small kernel.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <mutex>
@@ -23,11 +22,11 @@ namespace gqa {
 
 constexpr int kD = 128;                 // head dimension
 constexpr int kTile = 16;               // tokens per warp tile
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;                // one KV head per warp
 constexpr int kRing = 3;                // cp.async stages per warp
 constexpr int kTileBytes = kTile * kD * 2;          // 4 KiB for K, same for V
 constexpr int kWarpSmem = kRing * 2 * kTileBytes;    // 24 KiB
-constexpr int kSmemBytes = kWarps * kWarpSmem;       // 96 KiB per CTA: two CTAs per SM
+constexpr int kSmemBytes = kWarps * kWarpSmem;       // 192 KiB per CTA, one CTA per SM
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct Params {
@@ -77,33 +76,41 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 // Byte offset of (token row, 16-byte chunk) inside a swizzled [16][256 B] tile.
 __device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return uint32_t(row * 256 + ((chunk ^ (row & 7)) << 4)); }
 
-// Issues the copies of one 16-token tile of K and V for one KV head.
+// Issues the copies of one 16-token tile of K and V for one KV head.  Lane r (< 16) looks up the
+// page of token r once and passes the row's element offset round by shuffle, so the page-table
+// arithmetic (an integer division by the run-time page size) is done once per token, not per copy.
 __device__ __forceinline__ void load_tile(const Params& p, int b, int kvh, int tok0, int len, uint32_t k_smem,
                                           uint32_t v_smem, int lane) {
+  const int my_tok = tok0 + (lane & 15);
+  const bool my_valid = my_tok < len;
+  const int t = my_valid ? my_tok : 0;
+  const int page = __ldg(p.kv_indices + p.kv_indptr[b] + t / p.page_size);
+  const long long my_elem = (((long long)page * p.page_size + (t % p.page_size)) * p.hkv + kvh) * kD;
   const int chunk = lane & 15;
-  const int page_base = p.kv_indptr[b];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int row = (lane >> 4) + 2 * i;
-    const int tok = tok0 + row;
-    const bool valid = tok < len;
-    const int t = valid ? tok : 0;
-    const int page = __ldg(p.kv_indices + page_base + t / p.page_size);
-    const size_t elem = ((size_t(page) * p.page_size + (t % p.page_size)) * p.hkv + kvh) * kD + chunk * 8;
+    const long long elem = __shfl_sync(0xffffffffu, my_elem, row) + chunk * 8;
+    const bool valid = __shfl_sync(0xffffffffu, int(my_valid), row) != 0;
     cp_async_16(k_smem + tile_off(row, chunk), p.k_cache + elem, valid);
     cp_async_16(v_smem + tile_off(row, chunk), p.v_cache + elem, valid);
   }
 }
 
-__global__ void __launch_bounds__(kWarps * 32, 2)
+__global__ void __launch_bounds__(kWarps * 32, 1)
 gqa_decode_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int split = blockIdx.x, b = blockIdx.z;
   const int len = seq_len(p, b);
   const int begin = split * p.chunk;
   if (begin >= len) return;
   const int end = min(len, begin + p.chunk);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Warp w of the CTA owns KV head blockIdx.y*8 + w and walks the whole chunk: the eight warps read
+  // the eight heads' 256-byte pieces of the same tokens at about the same time, so the CTA streams
+  // whole pages (page_size * Hkv * 256 B contiguous) instead of scattered 256-byte pieces.
+  const int kvh = blockIdx.y * kWarps + warp;
+  if (kvh >= p.hkv) return;
   const int group = p.hq / p.hkv;
   const int row = lane >> 2;          // query head inside the group held by this lane's MMA rows
   const int quad = lane & 3;
@@ -125,22 +132,28 @@ gqa_decode_kernel(const Params p) {
   float m = -INFINITY, l = 0.f;       // running max (base 2) and sum of this lane's head row
 
   const uint32_t ring = smem_u32(smem) + warp * kWarpSmem;
-  const int tiles = (end - begin + kTile - 1) / kTile;
-  // warp w takes tiles w, w+4, ...
-  const int my_tiles = tiles > warp ? (tiles - warp + kWarps - 1) / kWarps : 0;
+  const int my_tiles = (end - begin + kTile - 1) / kTile;
 #pragma unroll
   for (int s = 0; s < kRing - 1; ++s) {
     if (s < my_tiles)
-      load_tile(p, b, kvh, begin + (warp + s * kWarps) * kTile, end, ring + s * 2 * kTileBytes,
+      load_tile(p, b, kvh, begin + s * kTile, end, ring + s * 2 * kTileBytes,
                 ring + s * 2 * kTileBytes + kTileBytes, lane);
     cp_async_commit();
   }
   for (int i = 0; i < my_tiles; ++i) {
     cp_async_wait<kRing - 2>();
-    __syncwarp();
+    __syncwarp();                     // tile i has landed; every lane is done with tile i-1
+    {
+      // the stage tile i-1 used is free: start the load that keeps kRing-1 tiles in flight
+      const int next = i + kRing - 1;
+      if (next < my_tiles)
+        load_tile(p, b, kvh, begin + next * kTile, end, ring + (next % kRing) * 2 * kTileBytes,
+                  ring + (next % kRing) * 2 * kTileBytes + kTileBytes, lane);
+      cp_async_commit();
+    }
     const int stage = i % kRing;
     const uint32_t k_smem = ring + stage * 2 * kTileBytes, v_smem = k_smem + kTileBytes;
-    const int tok0 = begin + (warp + i * kWarps) * kTile;
+    const int tok0 = begin + i * kTile;
 
     // S = Q K^T : two n-tiles of 8 tokens
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -194,46 +207,18 @@ gqa_decode_kernel(const Params p) {
       mma_bf16_16816(o[np * 2 + 1], pa0, 0u, pa2, 0u, b2, b3);
       mma_bf16_16816(o[np * 2 + 1], pb0, 0u, pb2, 0u, b2, b3);
     }
-    __syncwarp();
-    const int next = i + kRing - 1;
-    if (next < my_tiles)
-      load_tile(p, b, kvh, begin + (warp + next * kWarps) * kTile, end, ring + (next % kRing) * 2 * kTileBytes,
-                ring + (next % kRing) * 2 * kTileBytes + kTileBytes, lane);
-    cp_async_commit();
   }
   cp_async_wait<0>();
-  __syncthreads();
 
-  // ---- merge the four warps (shared memory reused: [warp][8 rows][D] fp32 + m + l) ----------
-  float* so = reinterpret_cast<float*>(smem);                 // [kWarps][8][kD]
-  float* sm = so + kWarps * 8 * kD;                           // [kWarps][8]
-  float* sl = sm + kWarps * 8;
-  if (row < 8) {
-#pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      so[(warp * 8 + row) * kD + n * 8 + quad * 2] = o[n][0];
-      so[(warp * 8 + row) * kD + n * 8 + quad * 2 + 1] = o[n][1];
-    }
-    if (quad == 0) { sm[warp * 8 + row] = m; sl[warp * 8 + row] = l; }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < group * kD; idx += blockDim.x) {
-    const int h = idx / kD, d = idx % kD;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, sm[w * 8 + h]);
-    float total = 0.f, acc = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-      const float mw = sm[w * 8 + h];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
-      total += sl[w * 8 + h] * f;
-      acc += so[(w * 8 + h) * kD + d] * f;
-    }
-    const int head = kvh * group + h;
+  // partial result of this (sequence, KV head, chunk): normalised rows and base-2 log-sum-exp
+  if (row < group) {
+    const int head = kvh * group + row;
     const size_t slot = (size_t(b) * p.max_splits + split) * p.hq + head;
-    p.part_o[slot * kD + d] = acc / total;
-    if (d == 0) p.part_lse[slot] = mm + log2f(total);
+    const float inv = 1.f / l;
+    float* dst = p.part_o + slot * kD + quad * 2;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0] * inv, o[n][1] * inv);
+    if (quad == 0) p.part_lse[slot] = m + log2f(l);
   }
 }
 
@@ -269,11 +254,12 @@ struct Handle {
 };
 
 inline int pick_chunk(const cake_b200_gqa_decode_config& c, int sms) {
-  // Aim for several CTAs per SM so that unequal sequence lengths even out; a chunk is a
-  // multiple of one round of the four warps (64 tokens).
-  int chunk = 512;
+  // One CTA per SM; aim for several rounds of CTAs so that unequal sequence lengths even out.  A
+  // chunk is a multiple of the 16-token tile.
+  int chunk = 1024;
   const long long max_len = c.max_kv_len > 0 ? c.max_kv_len : 1;
-  while (chunk > 64 && (long long)c.batch * c.num_kv_heads * ((max_len / 2 + chunk - 1) / chunk) < 12LL * sms) chunk >>= 1;
+  const long long head_blocks = (c.num_kv_heads + kWarps - 1) / kWarps;
+  while (chunk > 64 && (long long)c.batch * head_blocks * ((max_len / 2 + chunk - 1) / chunk) < 3LL * sms) chunk >>= 1;
   return chunk;
 }
 
@@ -346,7 +332,7 @@ extern "C" int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream) {
   if (p.batch == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
   CAKE_CUDA_OK(cudaMemsetAsync(h->status, 0, sizeof(int), s));
-  gqa::gqa_decode_kernel<<<dim3(p.max_splits, p.hkv, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
+  gqa::gqa_decode_kernel<<<dim3(p.max_splits, (p.hkv + gqa::kWarps - 1) / gqa::kWarps, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
   gqa::gqa_reduce_kernel<<<dim3(p.hq, p.batch), gqa::kD, 0, s>>>(p);
   return int(cudaGetLastError());
 }
@@ -447,7 +433,7 @@ extern "C" int cake_b200_gqa_decode_noalloc(void** buffers, const cake_b200_gqa_
   p.part_o = static_cast<float*>(scratch);
   p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.hq * gqa::kD;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
-  gqa::gqa_decode_kernel<<<dim3(p.max_splits, p.hkv, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
+  gqa::gqa_decode_kernel<<<dim3(p.max_splits, (p.hkv + gqa::kWarps - 1) / gqa::kWarps, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
   gqa::gqa_reduce_kernel<<<dim3(p.hq, p.batch), gqa::kD, 0, s>>>(p);
   return int(cudaGetLastError());
 }
