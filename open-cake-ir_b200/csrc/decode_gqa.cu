@@ -5,13 +5,21 @@
 // lse = logsumexp / ln 2; an empty sequence gives zeros and -inf.
 //
 // The kernel is bound by the HBM stream of K and V (2 * Hkv * D * 2 bytes per token) and never
-// writes logits or probabilities to memory.  A CTA owns (sequence, KV chunk); each of its eight warps
-// owns one KV head and runs its own cp.async ring over the chunk's 16-token tiles (128-bit copies, one 256-byte
-// row per token and head, XOR-swizzled in shared memory), so there is no CTA-wide barrier in
-// the main loop.  The G = Hq/Hkv query heads that share a KV head are the rows of an
-// m16n8k16 bf16 MMA (rows beyond G are zero): S = Q K^T via ldmatrix on the K tile, online
-// softmax in base 2 with warp shuffles, O += P V via ldmatrix.trans on the V tile (P as two bf16
-// terms, so the weights keep ~16 significant bits).  Chunks are merged by a second small kernel.
+// writes logits or probabilities to memory.  Work is cut into items (sequence, KV chunk, KV
+// head) that a one-CTA plan kernel lists on the device; the decode kernel is persistent, one CTA of
+// sixteen warps per SM, and each PAIR of warps (w, w+8) pulls items from an atomic queue on its
+// own, so the pairs of an SM drift apart and one pair's start-up and wind-down are covered by the
+// seven others' streaming.  The two warps of a pair take alternate 16-token tiles of the item and run
+// their own cp.async rings (128-bit copies, one 256-byte row per token and head, XOR-swizzled in
+// shared memory, K and V halves of a tile in separate slots); there is no CTA-wide barrier.
+// Neighbouring pairs start on neighbouring KV heads of the same tokens, which keeps the DRAM
+// accesses inside whole pages (page_size * Hkv * 256 B contiguous).  The G = Hq/Hkv query heads
+// that share a KV head are the rows of an m16n8k16 bf16 MMA for S = Q K^T (ldmatrix on the K tile;
+// rows beyond G are zero) and the columns of O^T += V^T P^T (ldmatrix.trans on the V tile; P as
+// two bf16 terms, so the weights keep ~16 significant bits); the online softmax runs in base 2
+// with warp shuffles.  The pair merges through shared memory and writes one partial result per
+// item; the pair that finishes the last item of a (sequence, KV head) merges its chunks and writes the
+// output, so there is no separate reduce launch.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <mutex>
@@ -22,12 +30,18 @@ namespace gqa {
 
 constexpr int kD = 128;                 // head dimension
 constexpr int kTile = 16;               // tokens per warp tile
-constexpr int kWarps = 8;                // one KV head per warp
-constexpr int kRing = 3;                // cp.async stages per warp
-constexpr int kTileBytes = kTile * kD * 2;          // 4 KiB for K, same for V
-constexpr int kWarpSmem = kRing * 2 * kTileBytes;    // 24 KiB
-constexpr int kSmemBytes = kWarps * kWarpSmem;       // 192 KiB per CTA, one CTA per SM
+constexpr int kHeads = 8;               // KV heads per CTA
+constexpr int kParts = 2;               // warps per KV head; warp part p takes tiles p, p+2, ...
+constexpr int kWarps = kHeads * kParts;
+constexpr int kSlots = 3;               // cp.async slots per warp, each one K or V half of a tile
+constexpr int kTileBytes = kTile * kD * 2;          // 4 KiB: 16 tokens of K (or of V) of one head
+constexpr int kWarpSmem = kSlots * kTileBytes;       // 12 KiB
+constexpr int kRingBytes = kWarps * kWarpSmem;       // 192 KiB per CTA, one CTA per SM
+constexpr int kParkBytes = 34 * 32 * 4;               // a warp's O^T (32 registers), m and l
+constexpr int kSmemBytes = kRingBytes + kHeads * (kParkBytes + 32);   // + per pair: parked state, 32-byte mailbox
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kGuideDiv = 2;            // guided chunk: half of what is left per worker ...
+constexpr int kGuideMin = 192;          // ... but at least 192 tokens: below that the per-item costs outweigh the balance
 
 struct Params {
   const __nv_bfloat16* q;        // [B, Hq, D]
@@ -39,9 +53,13 @@ struct Params {
   const float* sm_scale;         // [1]
   __nv_bfloat16* out;            // [B, Hq, D]
   float* lse;                    // [B, Hq]
-  float* part_o;                 // [B, splits, Hq, D] normalised partial outputs
-  float* part_lse;               // [B, splits, Hq]   base-2 partial log-sum-exp
-  int batch, hq, hkv, page_size, chunk, max_splits;
+  float* part_o;                 // [capacity, Hq, D] normalised partial outputs, one slot per entry of `items`
+  float* part_lse;               // [capacity, Hq]    base-2 partial log-sum-exp
+  int4* items;                   // [capacity] chunks of sequences, written by the plan kernel (see item_* below)
+  int* ctrl;                     // [0] work queue cursor, [1] number of entries of `items`
+  int* done;                     // [B, Hkv] finished items
+  int* status;                   // library status word (may be null)
+  int batch, hq, hkv, page_size, chunk, capacity, workers;
 };
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
@@ -49,9 +67,26 @@ __device__ __forceinline__ int seq_len(const Params& p, int b) {
   return pages <= 0 ? 0 : (pages - 1) * p.page_size + p.kv_last_page_len[b];
 }
 
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+// K and V are read exactly once: their lines are marked evict-first in L2, and the partial
+// results evict-last, so that the stream does not push the partial results out to DRAM before
+// they are merged.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid, uint64_t policy) {
   const int bytes = valid ? 16 : 0;     // 0 source bytes = zero fill
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(bytes), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void store_keep(float* dst, float value, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(dst), "f"(value), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -76,226 +111,509 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 // Byte offset of (token row, 16-byte chunk) inside a swizzled [16][256 B] tile.
 __device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return uint32_t(row * 256 + ((chunk ^ (row & 7)) << 4)); }
 
-// Issues the copies of one 16-token tile of K and V for one KV head.  Lane r (< 16) looks up the
-// page of token r once and passes the row's element offset round by shuffle, so the page-table
-// arithmetic (an integer division by the run-time page size) is done once per token, not per copy.
-__device__ __forceinline__ void load_tile(const Params& p, int b, int kvh, int tok0, int len, uint32_t k_smem,
-                                          uint32_t v_smem, int lane) {
-  const int my_tok = tok0 + (lane & 15);
-  const bool my_valid = my_tok < len;
-  const int t = my_valid ? my_tok : 0;
-  const int page = __ldg(p.kv_indices + p.kv_indptr[b] + t / p.page_size);
-  const long long my_elem = (((long long)page * p.page_size + (t % p.page_size)) * p.hkv + kvh) * kD;
+// Lane r (and r+16) looks up the page of token tok0+r once: the result is the index of that token's
+// 256-byte (token, head) row in the cache, or -1 beyond the sequence, so the page-table arithmetic
+// (an integer division by the run-time page size) is done once per token, not once per copy.
+__device__ __forceinline__ int lookup_rows(const Params& p, int page_base, int kvh, int tok0, int len, int lane) {
+  const int tok = tok0 + (lane & 15);
+  if (tok >= len) return -1;
+  const int page = __ldg(p.kv_indices + page_base + tok / p.page_size);
+  return (page * p.page_size + (tok % p.page_size)) * p.hkv + kvh;   // < 2^31 rows = 512 GiB per cache
+}
+
+// Issues the copies of the K (or V) half of a tile: 16 rows of 256 bytes, 16 lanes per row.
+__device__ __forceinline__ void load_half(const __nv_bfloat16* __restrict__ cache, int my_row, uint32_t dst, int lane,
+                                          uint64_t policy) {
   const int chunk = lane & 15;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int row = (lane >> 4) + 2 * i;
-    const long long elem = __shfl_sync(0xffffffffu, my_elem, row) + chunk * 8;
-    const bool valid = __shfl_sync(0xffffffffu, int(my_valid), row) != 0;
-    cp_async_16(k_smem + tile_off(row, chunk), p.k_cache + elem, valid);
-    cp_async_16(v_smem + tile_off(row, chunk), p.v_cache + elem, valid);
+    const int idx = __shfl_sync(0xffffffffu, my_row, row);
+    cp_async_16(dst + tile_off(row, chunk), cache + (size_t(idx < 0 ? 0 : idx) * kD + chunk * 8), idx >= 0, policy);
   }
+}
+
+// An entry of the work list is one chunk of one sequence:
+//   x = b | (chunks of b << 16),  y = (begin / 64) << 11 | tokens,  z = list index of b's first chunk,  w = kv_indptr[b].
+// Entry i owns partial-result slot i; with Hkv KV heads it stands for Hkv items of the queue.
+__device__ __forceinline__ int item_begin(const int4& r) { return (r.y >> 11) * 64; }
+__device__ __forceinline__ int item_tokens(const int4& r) { return r.y & 2047; }
+
+// Exclusive scan over the 1024 threads of the plan CTA; `total` receives the sum.
+template <typename T>
+__device__ __forceinline__ T plan_scan(T value, T* warp_sums, T& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T inc = value;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const T up = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += up;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {                      // the 32 warp totals: inclusive scan in place
+    T w = warp_sums[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const T up = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += up;
+    }
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  total = warp_sums[31];
+  const T before = warp > 0 ? warp_sums[warp - 1] : T(0);
+  __syncthreads();                      // warp_sums may be reused by the next scan
+  return before + inc - value;
+}
+
+// Chunk size for a sequence that starts when `remaining` tokens (over all sequences, in list
+// order) are still to be listed.  Guided sizes: a fixed share of what is left per worker, between
+// kGuideMin tokens and the base chunk, in multiples of 64 -- full-size chunks first, smaller ones
+// towards the end of the queue, so that the workers run dry at nearly the same time.
+__device__ __forceinline__ int chunk_at(const Params& p, long long remaining, bool guided, float share) {
+  if (!guided) return p.chunk;
+  const int c = int(fminf(float(remaining) * share, 4096.f)) & ~63;
+  return c < kGuideMin ? min(kGuideMin, p.chunk) : min(c, p.chunk);
+}
+
+// One CTA: lists the chunks of this launch, resets the queue and the counters, and writes the
+// results of empty sequences (zeros, lse = -inf), which no item covers.  All chunks of a sequence
+// have one size.  The kernel sits on the critical path of every decode step, so a batch of up to
+// 1024 sequences is planned in one sweep: one load round trip, two scans, the list.
+__global__ void __launch_bounds__(1024)
+gqa_plan_kernel(const Params p) {
+  __shared__ long long sums64[32];
+  __shared__ int sums32[32];
+  const int tid = threadIdx.x;
+#if __CUDA_ARCH__ >= 900
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the decode grid may take its SMs and wait
+#endif
+  if (tid == 0 && p.status) *p.status = 0;
+  const float share = float(p.hkv) / (float(p.workers) * float(kGuideDiv));   // of the remaining tokens: one chunk
+
+  const int len0 = tid < p.batch ? seq_len(p, tid) : 0;              // the first 1024 lengths stay in registers
+  long long mine = len0, all_tokens = 0;
+  for (int b = tid + 1024; b < p.batch; b += 1024) mine += seq_len(p, b);
+  plan_scan(mine, sums64, all_tokens);
+
+  bool guided = true;
+  for (int pass = 0; pass < 2; ++pass) {       // a second time only if the guided list does not fit
+    long long tokens_before = 0;
+    int entries_before = 0;
+    for (int base = 0; base < p.batch; base += 1024) {
+      const int b = base + tid;
+      const int len = base == 0 ? len0 : (b < p.batch ? seq_len(p, b) : 0);
+      long long batch_tokens = len;
+      long long start = tokens_before;
+      if (p.batch > 1024 || guided) start += plan_scan((long long)len, sums64, batch_tokens);
+      const int c = chunk_at(p, all_tokens - start, guided, share);
+      const int n = (len + c - 1) / c;
+      int batch_entries;
+      const int first = entries_before + plan_scan(n, sums32, batch_entries);
+      const bool fits = !guided || entries_before + batch_entries <= p.capacity;     // uniform for the CTA
+      if (fits && b < p.batch) {
+        // Entries written while a later batch turns out not to fit are simply written again.
+        const int page_base = p.kv_indptr[b];
+        for (int k = 0; k < n; ++k)
+          p.items[first + k] = make_int4(b | (n << 16), ((k * c / 64) << 11) | min(c, len - k * c), first, page_base);
+        for (int h = 0; h < p.hkv; ++h) p.done[size_t(b) * p.hkv + h] = 0;
+        if (len == 0) {
+          for (int h = 0; h < p.hq; ++h) {
+            p.lse[size_t(b) * p.hq + h] = -INFINITY;
+            for (int d = 0; d < kD; ++d) p.out[(size_t(b) * p.hq + h) * kD + d] = __float2bfloat16(0.f);
+          }
+        }
+      }
+      tokens_before += batch_tokens;
+      entries_before += batch_entries;
+      if (!fits) break;
+    }
+    if (!guided || entries_before <= p.capacity) {
+      if (tid == 0) {
+        p.ctrl[0] = p.workers;        // the first item of each worker follows from its index
+        p.ctrl[1] = entries_before;
+      }
+      break;
+    }
+    guided = false;
+  }
+}
+
+__device__ __forceinline__ void pair_barrier(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory"); }
+
+// Merges the chunks of (sequence b, KV head kvh): out = sum_s w_s o_s / sum_s w_s with
+// w_s = 2^(lse_s - max lse).  One warp works on all heads of the group at once: L lanes per head,
+// each owning 32/L float4 of the head's 128 dims, sixteen 16-byte loads in flight per lane, so
+// the merge costs a few memory round trips however many heads there are.  The partial results
+// were written by other SMs during this launch, so they are read past L1.
+template <int L>
+__device__ __forceinline__ void merge_chunks_t(const Params& p, int b, int kvh, int first, int chunks, int group, int lane) {
+  constexpr int NF = 32 / L;            // float4 per lane
+  constexpr int BATCH = 16 / NF;        // chunks in flight
+  const int hs = lane / L, sub = lane % L;
+  const bool have = hs < group;
+  const int head = kvh * group + (have ? hs : 0);
+  const size_t slot0 = size_t(first) * p.hq + head;                  // + s * hq
+  float mm = -INFINITY, total = 0.f;    // running maximum and sum of weights relative to it
+  float4 acc[NF];
+#pragma unroll
+  for (int k = 0; k < NF; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = 0; s0 < chunks; s0 += BATCH) {
+    float ls[BATCH];
+    float4 v[BATCH][NF];
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const int s = min(s0 + i, chunks - 1);            // past the end: the last row again, weight 0
+      ls[i] = __ldcg(p.part_lse + slot0 + size_t(s) * p.hq);
+      const float4* src = reinterpret_cast<const float4*>(p.part_o + (slot0 + size_t(s) * p.hq) * kD);
+#pragma unroll
+      for (int k = 0; k < NF; ++k) v[i][k] = __ldcg(src + sub + L * k);
+    }
+    float m_new = mm;                   // every chunk holds a token, so its lse is finite
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) m_new = fmaxf(m_new, ls[i]);
+    const float rescale = exp2f(mm - m_new);            // 0 on the first batch
+    mm = m_new;
+    total *= rescale;
+#pragma unroll
+    for (int k = 0; k < NF; ++k) { acc[k].x *= rescale; acc[k].y *= rescale; acc[k].z *= rescale; acc[k].w *= rescale; }
+#pragma unroll
+    for (int i = 0; i < BATCH; ++i) {
+      const float w = s0 + i < chunks ? exp2f(ls[i] - mm) : 0.f;
+      total += w;
+#pragma unroll
+      for (int k = 0; k < NF; ++k) {
+        acc[k].x += w * v[i][k].x; acc[k].y += w * v[i][k].y; acc[k].z += w * v[i][k].z; acc[k].w += w * v[i][k].w;
+      }
+    }
+  }
+  if (!have) return;
+  const float inv = 1.f / total;
+#pragma unroll
+  for (int k = 0; k < NF; ++k) {
+    uint2 packed;
+    packed.x = pack_bf16x2(acc[k].x * inv, acc[k].y * inv);
+    packed.y = pack_bf16x2(acc[k].z * inv, acc[k].w * inv);
+    *reinterpret_cast<uint2*>(p.out + (size_t(b) * p.hq + head) * kD + (sub + L * k) * 4) = packed;
+  }
+  if (sub == 0) p.lse[size_t(b) * p.hq + head] = mm + log2f(total);
+}
+
+__device__ __forceinline__ void merge_chunks(const Params& p, int b, int kvh, int first, int chunks, int group, int lane) {
+  if (group == 1) merge_chunks_t<32>(p, b, kvh, first, chunks, group, lane);
+  else if (group == 2) merge_chunks_t<16>(p, b, kvh, first, chunks, group, lane);
+  else if (group <= 4) merge_chunks_t<8>(p, b, kvh, first, chunks, group, lane);
+  else merge_chunks_t<4>(p, b, kvh, first, chunks, group, lane);
 }
 
 __global__ void __launch_bounds__(kWarps * 32, 1)
 gqa_decode_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int split = blockIdx.x, b = blockIdx.z;
-  const int len = seq_len(p, b);
-  const int begin = split * p.chunk;
-  if (begin >= len) return;
-  const int end = min(len, begin + p.chunk);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Warp w of the CTA owns KV head blockIdx.y*8 + w and walks the whole chunk: the eight warps read
-  // the eight heads' 256-byte pieces of the same tokens at about the same time, so the CTA streams
-  // whole pages (page_size * Hkv * 256 B contiguous) instead of scattered 256-byte pieces.
-  const int kvh = blockIdx.y * kWarps + warp;
-  if (kvh >= p.hkv) return;
+  const int pair = warp % kHeads, part = warp / kHeads;
   const int group = p.hq / p.hkv;
-  const int row = lane >> 2;          // query head inside the group held by this lane's MMA rows
+  const int row = lane >> 2;            // query head inside the group held by this lane's rows of S
   const int quad = lane & 3;
   const float scale2 = __ldg(p.sm_scale) * kLog2e;
+  const uint32_t ring = smem_u32(smem) + warp * kWarpSmem;
+  float* park = reinterpret_cast<float*>(smem + kRingBytes + pair * kParkBytes);
+  volatile int* mailbox = reinterpret_cast<volatile int*>(smem + kRingBytes + kHeads * kParkBytes + pair * 32);
 
-  // Q fragments (A operand): rows = heads of the group, zero beyond it.
+  const uint64_t stream_policy = l2_policy_evict_first(), keep_policy = l2_policy_evict_last();
+  // Launched as a programmatic dependent of the plan kernel: everything above overlaps it, the
+  // list and the counters are read only after it has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int total = p.ctrl[1] * p.hkv;  // items: entries of the list x KV heads, KV head fastest
+  // A pair's first item is fixed by its index; every later one is drawn from the queue while the
+  // item before it runs, by the first lane of the pair's first warp, which hands the answer to
+  // the second warp through the pair's mailbox in shared memory (words 0-4, then the item's
+  // serial number in word 5).
+  int idx = blockIdx.x * kHeads + pair;
+  int4 rec = make_int4(0, 0, 0, 0);
+  if (idx < total) rec = __ldg(p.items + idx / p.hkv);
+  if (part == 0 && lane == 0) mailbox[5] = -1;
+  __syncthreads();                      // the only CTA-wide barrier: every warp is still here
+  int serial = 0;
+  auto tiles_of = [&](int item, const int4& r) {    // tiles of an item that fall to this warp
+    return item < total ? ((item_tokens(r) + kTile - 1) / kTile - part + kParts - 1) / kParts : 0;
+  };
+  // Q fragments (A operand of S = Q K^T): rows = heads of the group, zero beyond it.
   uint32_t qa[8][2];
-  {
-    const __nv_bfloat16* qrow = p.q + (size_t(b) * p.hq + kvh * group + row) * kD;
+  auto load_q = [&](int item, const int4& r) {
+    const bool have = row < group && item < total;
+    const __nv_bfloat16* qrow = p.q + (size_t(r.x & 0xffff) * p.hq + (have ? (item % p.hkv) * group + row : 0)) * kD;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      qa[ks][0] = row < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + quad * 2) : 0u;
-      qa[ks][1] = row < group ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + quad * 2) : 0u;
+      qa[ks][0] = have ? __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + quad * 2)) : 0u;
+      qa[ks][1] = have ? __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + quad * 2)) : 0u;
     }
-  }
-  float o[16][4];
-#pragma unroll
-  for (int n = 0; n < 16; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-  float m = -INFINITY, l = 0.f;       // running max (base 2) and sum of this lane's head row
+  };
+  load_q(idx, rec);
 
-  const uint32_t ring = smem_u32(smem) + warp * kWarpSmem;
-  const int my_tiles = (end - begin + kTile - 1) / kTile;
-#pragma unroll
-  for (int s = 0; s < kRing - 1; ++s) {
-    if (s < my_tiles)
-      load_tile(p, b, kvh, begin + s * kTile, end, ring + s * 2 * kTileBytes,
-                ring + s * 2 * kTileBytes + kTileBytes, lane);
-    cp_async_commit();
-  }
-  for (int i = 0; i < my_tiles; ++i) {
-    cp_async_wait<kRing - 2>();
-    __syncwarp();                     // tile i has landed; every lane is done with tile i-1
-    {
-      // the stage tile i-1 used is free: start the load that keeps kRing-1 tiles in flight
-      const int next = i + kRing - 1;
-      if (next < my_tiles)
-        load_tile(p, b, kvh, begin + next * kTile, end, ring + (next % kRing) * 2 * kTileBytes,
-                  ring + (next % kRing) * 2 * kTileBytes + kTileBytes, lane);
+  // A warp's tiles form one stream across its items.  Copy groups alternate K(t), V(t), K(t+1),
+  // ... through three 4 KiB slots: two are in flight while the third is being consumed, also
+  // across the boundary between two items (`primed`: the first tile of the coming item is on
+  // its way already).
+  int k_slot = 0;
+  int next_row = -1;
+  bool primed = false;
+
+  while (idx < total) {
+    const int kvh = idx % p.hkv;
+    const int b = rec.x & 0xffff, chunks = int(unsigned(rec.x) >> 16);
+    const int begin = item_begin(rec), end = begin + item_tokens(rec), page_base = rec.w;
+    const int my_tiles = tiles_of(idx, rec);
+    // Next item: drawn now, its record fetched one tile later and published one tile after that,
+    // so that neither memory round trip stalls the stream; both warps need it at their last tile,
+    // where the first copies of the next item go out.
+    int drawn_idx = total;
+    int4 drawn_rec = make_int4(0, 0, 0, 0);
+    if (part == 0 && lane == 0) drawn_idx = atomicAdd(p.ctrl, 1);
+    int nxt_idx = total;
+    int4 nxt_rec = make_int4(0, 0, 0, 0);
+    bool know_next = false;
+    if (my_tiles > 0 && !primed) {      // cold start: nothing of this item is in flight yet
+      const int v_slot = k_slot == 2 ? 0 : k_slot + 1;
+      next_row = lookup_rows(p, page_base, kvh, begin + part * kTile, end, lane);
+      load_half(p.k_cache, next_row, ring + k_slot * kTileBytes, lane, stream_policy);
+      cp_async_commit();
+      load_half(p.v_cache, next_row, ring + v_slot * kTileBytes, lane, stream_policy);
       cp_async_commit();
     }
-    const int stage = i % kRing;
-    const uint32_t k_smem = ring + stage * 2 * kTileBytes, v_smem = k_smem + kTileBytes;
-    const int tok0 = begin + i * kTile;
+    primed = false;
 
-    // S = Q K^T : two n-tiles of 8 tokens
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    // O is kept transposed, O^T[dim][head] = V^T P^T, so that all four accumulator registers of
+    // an MMA are live (dims are the 16 rows, the group's heads the 8 columns): o[n] covers dims
+    // n*16 + lane/4 (+8 for registers 2, 3) and heads quad*2 (+1 for registers 1, 3).
+    float o[8][4];
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      uint32_t b0, b1, b2, b3;
-      const int mi = lane >> 3;                         // which 8x8 matrix this lane addresses
-      const int trow = (mi >> 1) * 8 + (lane & 7);
-      ldmatrix_x4(k_smem + tile_off(trow, ks * 2 + (mi & 1)), b0, b1, b2, b3);
-      mma_bf16_16816(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-      mma_bf16_16816(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+    for (int n = 0; n < 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m = -INFINITY, l = 0.f;       // running max (base 2) and sum of head `row`
+
+    for (int j = 0; j < my_tiles; ++j) {
+      const int v_slot = k_slot == 2 ? 0 : k_slot + 1;
+      const int free_slot = v_slot == 2 ? 0 : v_slot + 1;     // held the V half of the previous tile
+      const int tok0 = begin + (part + j * kParts) * kTile;
+      // the tile after this one in the stream: the item's next, or the first of the coming item
+      const bool last = j + 1 == my_tiles;
+      if (part == 0) {
+        if (j == min(1, my_tiles - 1) && lane == 0 && drawn_idx < total) drawn_rec = __ldg(p.items + drawn_idx / p.hkv);
+        if (j == min(2, my_tiles - 1) && lane == 0) {
+          mailbox[0] = drawn_rec.x; mailbox[1] = drawn_rec.y; mailbox[2] = drawn_rec.z; mailbox[3] = drawn_rec.w;
+          mailbox[4] = drawn_idx;
+          __threadfence_block();
+          mailbox[5] = serial;
+        }
+      }
+      if (last) {
+        if (part == 0) {
+          nxt_idx = __shfl_sync(0xffffffffu, drawn_idx, 0);
+          nxt_rec = make_int4(__shfl_sync(0xffffffffu, drawn_rec.x, 0), __shfl_sync(0xffffffffu, drawn_rec.y, 0),
+                              __shfl_sync(0xffffffffu, drawn_rec.z, 0), __shfl_sync(0xffffffffu, drawn_rec.w, 0));
+          know_next = true;
+        } else {
+          // Normally published long ago.  If not, go on without the early copies: the record is
+          // read again behind the pair's barrier below.
+          for (int spin = 0; spin < 4096 && !know_next; ++spin) know_next = mailbox[5] == serial;
+          if (know_next) {
+            __threadfence_block();
+            nxt_rec = make_int4(mailbox[0], mailbox[1], mailbox[2], mailbox[3]);
+            nxt_idx = mailbox[4];
+          }
+        }
+      }
+      const int nxt_tiles = know_next ? tiles_of(nxt_idx, nxt_rec) : 0;
+      const bool follows = !last || nxt_tiles > 0;
+      cp_async_wait<1>();
+      __syncwarp();                     // K(t) has landed; every lane is done with V(t-1)
+      if (follows) {
+        next_row = last ? lookup_rows(p, nxt_rec.w, nxt_idx % p.hkv, item_begin(nxt_rec) + part * kTile,
+                                      item_begin(nxt_rec) + item_tokens(nxt_rec), lane)
+                        : lookup_rows(p, page_base, kvh, tok0 + kParts * kTile, end, lane);
+        load_half(p.k_cache, next_row, ring + free_slot * kTileBytes, lane, stream_policy);
+      }
+      cp_async_commit();
+      const uint32_t k_smem = ring + k_slot * kTileBytes, v_smem = ring + v_slot * kTileBytes;
+
+      // S = Q K^T : two n-tiles of 8 tokens
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        const int mi = lane >> 3;                       // which 8x8 matrix this lane addresses
+        const int trow = (mi >> 1) * 8 + (lane & 7);
+        ldmatrix_x4(k_smem + tile_off(trow, ks * 2 + (mi & 1)), b0, b1, b2, b3);
+        mma_bf16_16816(s0, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+        mma_bf16_16816(s1, qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+      }
+      // this lane: head `row`, tokens tok0 + quad*2 + {0,1} (s0) and + 8 (s1)
+      float v[4];
+      v[0] = s0[0] * scale2; v[1] = s0[1] * scale2; v[2] = s1[0] * scale2; v[3] = s1[1] * scale2;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int tok = tok0 + quad * 2 + (i & 1) + (i >> 1) * 8;
+        if (tok >= end) v[i] = -INFINITY;
+      }
+      float tmax = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      const float m_new = fmaxf(m, tmax);            // finite: every tile holds at least one valid token
+      const float alpha = exp2f(m - m_new);
+      float pr[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pr[i] = exp2f(v[i] - m_new);
+      float psum = pr[0] + pr[1] + pr[2] + pr[3];
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      l = l * alpha + psum;
+      m = m_new;
+      // P enters the tensor core as two bf16 terms (value + rounding residual): a single bf16
+      // term would put 2^-9 relative error on every weight, more than the contract's tolerance
+      // allows once the weighted values cancel.  As the B operand of O^T += V^T P^T the fragment
+      // layout of P^T (tokens quad*2.. of head lane/4) is exactly the accumulator layout of S.
+      uint32_t p_hi0, p_hi1, p_lo0, p_lo1;
+      split_bf16x2(pr[0], pr[1], p_hi0, p_lo0);       // tokens 0..7 of the tile
+      split_bf16x2(pr[2], pr[3], p_hi1, p_lo1);       // tokens 8..15
+      const float alpha0 = __shfl_sync(0xffffffffu, alpha, quad * 8);       // head quad*2
+      const float alpha1 = __shfl_sync(0xffffffffu, alpha, quad * 8 + 4);   // head quad*2 + 1
+
+      cp_async_wait<1>();
+      __syncwarp();                     // V(t) has landed; every lane is done with K(t)
+      if (follows) load_half(p.v_cache, next_row, ring + k_slot * kTileBytes, lane, stream_policy);
+      cp_async_commit();
+#pragma unroll
+      for (int n = 0; n < 8; ++n) { o[n][0] *= alpha0; o[n][1] *= alpha1; o[n][2] *= alpha0; o[n][3] *= alpha1; }
+      // V^T fragments through ldmatrix.trans: 16 dims x 16 tokens per instruction
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        uint32_t a0, a1, a2, a3;
+        const int mi = lane >> 3;
+        const int trow = (mi >> 1) * 8 + (lane & 7);    // matrices 0/1: tokens 0-7, dims +0/+8; 2/3: tokens 8-15
+        ldmatrix_x4_trans(v_smem + tile_off(trow, n * 2 + (mi & 1)), a0, a1, a2, a3);
+        mma_bf16_16816(o[n], a0, a1, a2, a3, p_hi0, p_hi1);
+        mma_bf16_16816(o[n], a0, a1, a2, a3, p_lo0, p_lo1);
+      }
+      k_slot = free_slot;
+      primed = last && follows;
     }
-    // this lane: row `row`, tokens tok0 + quad*2 + {0,1} (s0) and + 8 (s1)
-    float v[4];
-    v[0] = s0[0] * scale2; v[1] = s0[1] * scale2; v[2] = s1[0] * scale2; v[3] = s1[1] * scale2;
+    if (know_next) load_q(nxt_idx, nxt_rec);   // the Q registers are free: fetch the coming item's
+
+    if (part == 1) {                    // the second warp parks its state for the first
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int tok = tok0 + quad * 2 + (j & 1) + (j >> 1) * 8;
-      if (tok >= end) v[j] = -INFINITY;
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) park[(n * 4 + r) * 32 + lane] = o[n][r];
+      park[32 * 32 + lane] = m;
+      park[33 * 32 + lane] = l;
     }
-    float tmax = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-    const float m_new = fmaxf(m, tmax);              // finite: every tile holds at least one valid token
-    const float alpha = exp2f(m - m_new);
-    float pr[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) pr[j] = exp2f(v[j] - m_new);
-    float psum = pr[0] + pr[1] + pr[2] + pr[3];
-    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-    l = l * alpha + psum;
-    m = m_new;
-    // P enters the tensor core as two bf16 terms (value + rounding residual): a single bf16 term
-    // would put 2^-9 relative error on every weight, more than the contract's tolerance allows
-    // once the weighted values cancel.
-    uint32_t pa0, pa2, pb0, pb2;
-    split_bf16x2(pr[0], pr[1], pa0, pb0);             // tokens 0..7 of the tile  (A cols k..k+1)
-    split_bf16x2(pr[2], pr[3], pa2, pb2);             // tokens 8..15             (A cols k+8..)
-#pragma unroll
-    for (int n = 0; n < 16; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
-    // O += P V : V^T fragments through ldmatrix.trans, 16 dims per instruction
-#pragma unroll
-    for (int np = 0; np < 8; ++np) {
-      uint32_t b0, b1, b2, b3;
-      const int mi = lane >> 3;
-      const int trow = (mi & 1) * 8 + (lane & 7);       // matrices 0/1: tokens 0-7 / 8-15; 2/3: next 8 dims
-      ldmatrix_x4_trans(v_smem + tile_off(trow, np * 2 + (mi >> 1)), b0, b1, b2, b3);
-      mma_bf16_16816(o[np * 2], pa0, 0u, pa2, 0u, b0, b1);
-      mma_bf16_16816(o[np * 2], pb0, 0u, pb2, 0u, b0, b1);
-      mma_bf16_16816(o[np * 2 + 1], pa0, 0u, pa2, 0u, b2, b3);
-      mma_bf16_16816(o[np * 2 + 1], pb0, 0u, pb2, 0u, b2, b3);
+    pair_barrier(pair);                 // parked state and mailbox are written
+    if (!know_next) {                   // a warp without tiles in this item, or one that gave up waiting
+      nxt_rec = make_int4(mailbox[0], mailbox[1], mailbox[2], mailbox[3]);
+      nxt_idx = mailbox[4];
+      load_q(nxt_idx, nxt_rec);
     }
+    float f00 = 0.f, f01 = 0.f, f10 = 0.f, f11 = 0.f;
+    if (part == 0) {                    // fold the partner's state into the registers
+      const float m1 = park[32 * 32 + lane], l1 = park[33 * 32 + lane];
+      const float m_all = fmaxf(m, m1);            // m is finite: the first warp always has a tile
+      const float w0 = exp2f(m - m_all), w1 = exp2f(m1 - m_all);
+      l = l * w0 + l1 * w1;
+      m = m_all;
+      const float inv = 1.f / l;
+      f00 = __shfl_sync(0xffffffffu, w0 * inv, quad * 8); f01 = __shfl_sync(0xffffffffu, w0 * inv, quad * 8 + 4);
+      f10 = __shfl_sync(0xffffffffu, w1 * inv, quad * 8); f11 = __shfl_sync(0xffffffffu, w1 * inv, quad * 8 + 4);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        o[n][0] = o[n][0] * f00 + park[(n * 4 + 0) * 32 + lane] * f10;
+        o[n][1] = o[n][1] * f01 + park[(n * 4 + 1) * 32 + lane] * f11;
+        o[n][2] = o[n][2] * f00 + park[(n * 4 + 2) * 32 + lane] * f10;
+        o[n][3] = o[n][3] * f01 + park[(n * 4 + 3) * 32 + lane] * f11;
+      }
+    }
+    pair_barrier(pair);                 // parked state and mailbox have been read
+    if (part == 0) {
+      // partial result of this item: normalised rows and base-2 log-sum-exp
+      const size_t slot0 = size_t(idx / p.hkv) * p.hq + kvh * group;
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int dim = n * 16 + row;
+        if (quad * 2 < group) {
+          store_keep(p.part_o + (slot0 + quad * 2) * kD + dim, o[n][0], keep_policy);
+          store_keep(p.part_o + (slot0 + quad * 2) * kD + dim + 8, o[n][2], keep_policy);
+        }
+        if (quad * 2 + 1 < group) {
+          store_keep(p.part_o + (slot0 + quad * 2 + 1) * kD + dim, o[n][1], keep_policy);
+          store_keep(p.part_o + (slot0 + quad * 2 + 1) * kD + dim + 8, o[n][3], keep_policy);
+        }
+      }
+      if (row < group && quad == 0) store_keep(p.part_lse + slot0 + row, m + log2f(l), keep_policy);
+      // The pair that completes the last item of (b, kvh) merges the chunks.
+      __threadfence();
+      __syncwarp();
+      int last_item = 0;
+      if (lane == 0) last_item = atomicAdd(p.done + size_t(b) * p.hkv + kvh, 1) == chunks - 1;
+      if (__shfl_sync(0xffffffffu, last_item, 0)) {
+        __threadfence();
+        merge_chunks(p, b, kvh, rec.z, chunks, group, lane);
+      }
+    }
+    idx = nxt_idx; rec = nxt_rec;
+    ++serial;
   }
   cp_async_wait<0>();
-
-  // partial result of this (sequence, KV head, chunk): normalised rows and base-2 log-sum-exp
-  if (row < group) {
-    const int head = kvh * group + row;
-    const size_t slot = (size_t(b) * p.max_splits + split) * p.hq + head;
-    const float inv = 1.f / l;
-    float* dst = p.part_o + slot * kD + quad * 2;
-#pragma unroll
-    for (int n = 0; n < 16; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0] * inv, o[n][1] * inv);
-    if (quad == 0) p.part_lse[slot] = m + log2f(l);
-  }
-}
-
-// One CTA per (sequence, query head): merges the chunks' partial results.
-__global__ void __launch_bounds__(kD)
-gqa_reduce_kernel(const Params p) {
-  const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int len = seq_len(p, b);
-  const size_t o_idx = (size_t(b) * p.hq + head) * kD + d;
-  if (len == 0) {
-    p.out[o_idx] = __float2bfloat16(0.f);
-    if (d == 0) p.lse[size_t(b) * p.hq + head] = -INFINITY;
-    return;
-  }
-  const int splits = (len + p.chunk - 1) / p.chunk;
-  float mm = -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p.part_lse[(size_t(b) * p.max_splits + s) * p.hq + head]);
-  float total = 0.f, acc = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const size_t slot = (size_t(b) * p.max_splits + s) * p.hq + head;
-    const float w = exp2f(p.part_lse[slot] - mm);
-    total += w;
-    acc += w * p.part_o[slot * kD + d];
-  }
-  p.out[o_idx] = __float2bfloat16(acc / total);
-  if (d == 0) p.lse[size_t(b) * p.hq + head] = mm + log2f(total);
 }
 
 struct Handle {
   int device;
   Params p;
-  int* status;      // first word of the workspace; this operator has no device-side waits, it stays 0
 };
 
 inline int pick_chunk(const cake_b200_gqa_decode_config& c, int sms) {
-  // One CTA per SM; aim for several rounds of CTAs so that unequal sequence lengths even out.  A
-  // chunk is a multiple of the 16-token tile.
-  int chunk = 1024;
+  // Base chunk: the size of the items at the head of the queue (the plan kernel shrinks them
+  // towards its end).  Long enough that the per-item costs (merge of the two warps, partial
+  // result, counter) vanish, short enough that even base-size chunks alone would give every warp
+  // pair a few items on sequences of half the maximum length.  A multiple of 64 tokens.
+  int chunk = 512;
   const long long max_len = c.max_kv_len > 0 ? c.max_kv_len : 1;
-  const long long head_blocks = (c.num_kv_heads + kWarps - 1) / kWarps;
-  while (chunk > 64 && (long long)c.batch * head_blocks * ((max_len / 2 + chunk - 1) / chunk) < 3LL * sms) chunk >>= 1;
+  while (chunk > 64 && (long long)c.batch * c.num_kv_heads * ((max_len / 2 + chunk - 1) / chunk) < 2LL * kHeads * sms) chunk >>= 1;
   return chunk;
 }
 
-}  // namespace gqa
-}  // namespace cake
-
-static bool gqa_config_ok(const cake_b200_gqa_decode_config& c) {
-  if (c.batch < 0 || c.batch > 65535 || c.head_dim != cake::gqa::kD || c.page_size <= 0 || c.max_kv_len < 0) return false;
-  if (c.num_kv_heads <= 0 || c.num_kv_heads > 65535 || c.num_qo_heads % c.num_kv_heads) return false;
-  const int g = c.num_qo_heads / c.num_kv_heads;
-  return g >= 1 && g <= 8;
+// Entries of the work list that always suffice with base-size chunks, and the room that lets the
+// plan kernel use guided sizes (about 16 smaller chunks per worker near the end of the queue).
+inline size_t uniform_entries(const cake_b200_gqa_decode_config& c, int chunk) {
+  return size_t(c.batch) * (size_t((c.max_kv_len + chunk - 1) / chunk) + 1);
+}
+inline size_t guided_entries(const cake_b200_gqa_decode_config& c, int chunk) {
+  return uniform_entries(c, chunk) + size_t(16 * kHeads * 148) / c.num_kv_heads + 64;
 }
 
-extern "C" size_t cake_b200_gqa_decode_workspace_bytes(const cake_b200_gqa_decode_config* c) {
-  if (!c || !gqa_config_ok(*c)) return 0;
-  const int chunk = cake::gqa::pick_chunk(*c, 148);
-  const size_t splits = size_t((c->max_kv_len + chunk - 1) / chunk) + 1;
-  const size_t slots = size_t(c->batch) * splits * c->num_qo_heads;
-  return 256 + slots * (cake::gqa::kD + 1) * sizeof(float) + 256;
+// Scratch layout shared by the two entry points (offsets from a 256-byte aligned base):
+//   [0, 256)  ctrl   | done [B*Hkv] int | items [entries] int4 | part_o [entries*Hq*D] f32 | part_lse [entries*Hq] f32
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+inline size_t scratch_bytes(const cake_b200_gqa_decode_config& c, size_t entries) {
+  return 256 + align256(size_t(c.batch) * c.num_kv_heads * sizeof(int)) + align256(entries * sizeof(int4)) +
+         align256(entries * c.num_qo_heads * kD * sizeof(float)) + align256(entries * c.num_qo_heads * sizeof(float));
+}
+inline void carve_scratch(Params& p, uint8_t* base) {
+  const size_t entries = size_t(p.capacity);
+  p.ctrl = reinterpret_cast<int*>(base);
+  base += 256;
+  p.done = reinterpret_cast<int*>(base);
+  base += align256(size_t(p.batch) * p.hkv * sizeof(int));
+  p.items = reinterpret_cast<int4*>(base);
+  base += align256(entries * sizeof(int4));
+  p.part_o = reinterpret_cast<float*>(base);
+  base += align256(entries * p.hq * kD * sizeof(float));
+  p.part_lse = reinterpret_cast<float*>(base);
 }
 
-extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_decode_config* config, void** handle_out) {
-  using namespace cake;
-  if (!buffers || !config || !handle_out) return kErrBadArgument;
-  *handle_out = nullptr;
-  int device = 0;
-  if (int rc = require_blackwell(&device)) return rc;
-  if (!gqa_config_ok(*config)) return kErrBadArgument;
-  for (int i = 0; i < 10; ++i) {
+inline int fill_params(Params& p, void** buffers, const cake_b200_gqa_decode_config& c) {
+  for (int i = 0; i < 9; ++i) {
     if (!buffers[i]) return kErrBadArgument;
     if (i <= 2 && (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
   }
-  auto* h = new (std::nothrow) gqa::Handle;
-  if (!h) return int(cudaErrorMemoryAllocation);
-  h->device = device;
-  gqa::Params& p = h->p;
   p.q = static_cast<const __nv_bfloat16*>(buffers[0]);
   p.k_cache = static_cast<const __nv_bfloat16*>(buffers[1]);
   p.v_cache = static_cast<const __nv_bfloat16*>(buffers[2]);
@@ -305,18 +623,85 @@ extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_d
   p.sm_scale = static_cast<const float*>(buffers[6]);
   p.out = static_cast<__nv_bfloat16*>(buffers[7]);
   p.lse = static_cast<float*>(buffers[8]);
-  p.batch = int(config->batch);
-  p.hq = config->num_qo_heads;
-  p.hkv = config->num_kv_heads;
-  p.page_size = config->page_size;
+  p.batch = int(c.batch);
+  p.hq = c.num_qo_heads;
+  p.hkv = c.num_kv_heads;
+  p.page_size = c.page_size;
+  p.status = nullptr;
+  return 0;
+}
+
+// One persistent CTA per SM, but never more workers than there can be items.
+inline int grid_for(const Params& p, int sms) {
+  const long long items = (long long)p.capacity * p.hkv;
+  const long long ctas = (items + kHeads - 1) / kHeads;
+  return int(ctas < sms ? (ctas < 1 ? 1 : ctas) : sms);
+}
+
+inline int launch(Params& p, int sms, cudaStream_t s) {
+  const int grid = grid_for(p, sms);
+  p.workers = grid * kHeads;
+  gqa_plan_kernel<<<1, 1024, 0, s>>>(p);
+  // The decode grid is a programmatic dependent: it may start while the plan kernel runs and waits
+  // for it on the device, which takes the second launch latency off the critical path.
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kWarps * 32);
+  config.dynamicSmemBytes = kSmemBytes;
+  config.stream = s;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, gqa_decode_kernel, p);
+  return int(err != cudaSuccess ? err : cudaGetLastError());
+}
+
+}  // namespace gqa
+}  // namespace cake
+
+static bool gqa_config_ok(const cake_b200_gqa_decode_config& c) {
+  if (c.batch < 0 || c.batch > 65535 || c.head_dim != cake::gqa::kD || c.page_size <= 0 || c.max_kv_len < 0) return false;
+  if (c.max_kv_len > (1 << 21)) return false;             // at most 2^15 chunks of 64 tokens per sequence
+  if (c.num_kv_heads <= 0 || c.num_kv_heads > 65535 || c.num_qo_heads % c.num_kv_heads) return false;
+  const int g = c.num_qo_heads / c.num_kv_heads;
+  return g >= 1 && g <= 8;
+}
+
+static int gqa_sm_count(int device, int* sms) {
+  CAKE_CUDA_OK(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, device));
+  return 0;
+}
+
+extern "C" size_t cake_b200_gqa_decode_workspace_bytes(const cake_b200_gqa_decode_config* c) {
+  if (!c || !gqa_config_ok(*c)) return 0;
+  return 256 + cake::gqa::scratch_bytes(*c, cake::gqa::guided_entries(*c, cake::gqa::pick_chunk(*c, 148))) + 256;
+}
+
+extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_decode_config* config, void** handle_out) {
+  using namespace cake;
+  if (!buffers || !config || !handle_out) return kErrBadArgument;
+  *handle_out = nullptr;
+  int device = 0;
+  if (int rc = require_blackwell(&device)) return rc;
+  if (!gqa_config_ok(*config) || !buffers[9]) return kErrBadArgument;
+  auto* h = new (std::nothrow) gqa::Handle;
+  if (!h) return int(cudaErrorMemoryAllocation);
+  h->device = device;
+  gqa::Params& p = h->p;
+  if (int rc = gqa::fill_params(p, buffers, *config)) { delete h; return rc; }
   p.chunk = gqa::pick_chunk(*config, 148);
-  p.max_splits = int((config->max_kv_len + p.chunk - 1) / p.chunk) + 1;
-  h->status = static_cast<int*>(buffers[9]);
+  p.capacity = int(gqa::guided_entries(*config, p.chunk));
+  p.status = static_cast<int*>(buffers[9]);               // first word of the workspace
   uint8_t* ws = static_cast<uint8_t*>(buffers[9]) + 256;
-  p.part_o = reinterpret_cast<float*>(ws);
-  p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.hq * gqa::kD;
-  int rc = int(cudaFuncSetAttribute(gqa::gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gqa::kSmemBytes));
+  ws += (256 - (reinterpret_cast<uintptr_t>(ws) & 255)) & 255;
+  gqa::carve_scratch(p, ws);
+  int sms = 0;
+  int rc = gqa_sm_count(device, &sms);
+  if (!rc) rc = int(cudaFuncSetAttribute(gqa::gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gqa::kSmemBytes));
   if (rc) { delete h; return rc; }
+  p.workers = sms;                                        // the SM count until launch turns it into workers
   *handle_out = h;
   return 0;
 }
@@ -328,13 +713,9 @@ extern "C" int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream) {
   int device = -1;
   CAKE_CUDA_OK(cudaGetDevice(&device));
   if (device != h->device) return kErrWrongDevice;
-  const gqa::Params& p = h->p;
-  if (p.batch == 0) return 0;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
-  CAKE_CUDA_OK(cudaMemsetAsync(h->status, 0, sizeof(int), s));
-  gqa::gqa_decode_kernel<<<dim3(p.max_splits, (p.hkv + gqa::kWarps - 1) / gqa::kWarps, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
-  gqa::gqa_reduce_kernel<<<dim3(p.hq, p.batch), gqa::kD, 0, s>>>(p);
-  return int(cudaGetLastError());
+  if (h->p.batch == 0) return 0;
+  gqa::Params p = h->p;
+  return gqa::launch(p, h->p.workers, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 extern "C" int cake_b200_gqa_decode_destroy(void* handle) {
@@ -349,14 +730,16 @@ extern "C" int cake_b200_gqa_decode_destroy(void* handle) {
 // pool already owns the whole of device memory (a cudaMalloc there fails or fragments the pool),
 // a plug-in sandbox that forbids allocator calls from plug-in code, or a latency-critical loop that
 // cannot afford the device-wide synchronisation an allocation may imply.  They also cannot hand us
-// a workspace they do not have.  For them the split-KV partial results live in the fixed array
-// below, which is part of the library image: every GPU that loads the library carries these
-// 16 MiB until the process exits, whether or not the entry point is ever called.
+// a workspace they do not have.  For them the work list, the counters and the split-KV partial
+// results live in the fixed array below, which is part of the library image: every GPU that loads
+// the library carries these 16 MiB until the process exits, whether or not the entry point is ever
+// called.
 //
-// All calls share the array and nothing clears it between calls: the reduce kernel reads only
-// the slots the decode kernel of the same call has just written, so stale contents are never
-// consumed and nothing needs to start at zero.  Two calls that overlap on the GPU (different
-// streams, or different host threads) race on it -- serialise them.
+// All calls share the array and nothing clears it between calls: the plan kernel of a call
+// rewrites the queue, the counters and the work list before the decode kernel of the same call
+// reads them, and a partial result is read only after the same call has written it, so stale
+// contents are never consumed and nothing needs to start at zero.  Two calls that overlap on the
+// GPU (different streams, or different host threads) race on it -- serialise them.
 // ------------------------------------------------------------------------------------------
 namespace cake {
 namespace gqa {
@@ -399,41 +782,24 @@ extern "C" int cake_b200_gqa_decode_noalloc(void** buffers, const cake_b200_gqa_
   int device = 0;
   if (int rc = require_blackwell(&device)) return rc;
   if (!gqa_config_ok(*config)) return kErrBadArgument;
-  for (int i = 0; i < 9; ++i) {
-    if (!buffers[i]) return kErrBadArgument;
-    if (i <= 2 && (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
-  }
   gqa::Params p;
-  p.q = static_cast<const __nv_bfloat16*>(buffers[0]);
-  p.k_cache = static_cast<const __nv_bfloat16*>(buffers[1]);
-  p.v_cache = static_cast<const __nv_bfloat16*>(buffers[2]);
-  p.kv_indptr = static_cast<const int*>(buffers[3]);
-  p.kv_indices = static_cast<const int*>(buffers[4]);
-  p.kv_last_page_len = static_cast<const int*>(buffers[5]);
-  p.sm_scale = static_cast<const float*>(buffers[6]);
-  p.out = static_cast<__nv_bfloat16*>(buffers[7]);
-  p.lse = static_cast<float*>(buffers[8]);
-  p.batch = int(config->batch);
-  p.hq = config->num_qo_heads;
-  p.hkv = config->num_kv_heads;
-  p.page_size = config->page_size;
+  if (int rc = gqa::fill_params(p, buffers, *config)) return rc;
   if (p.batch == 0) return 0;
   // Same chunking as the workspace variant; longer chunks (fewer partial results) if that is what
   // it takes to fit the fixed scratch, and a refusal if even two chunks per sequence do not fit.
   p.chunk = gqa::pick_chunk(*config, 148);
-  auto bytes_needed = [&](int chunk) {
-    const size_t splits = size_t((config->max_kv_len + chunk - 1) / chunk) + 1;
-    return size_t(p.batch) * splits * p.hq * (gqa::kD + 1) * sizeof(float);
-  };
-  while (bytes_needed(p.chunk) > gqa::kNoAllocScratchBytes && p.chunk < config->max_kv_len) p.chunk *= 2;
-  if (bytes_needed(p.chunk) > gqa::kNoAllocScratchBytes) return kErrWorkspace;   // batch * heads too large for 16 MiB
-  p.max_splits = int((config->max_kv_len + p.chunk - 1) / p.chunk) + 1;
+  while (gqa::scratch_bytes(*config, gqa::uniform_entries(*config, p.chunk)) > gqa::kNoAllocScratchBytes && p.chunk < config->max_kv_len &&
+         p.chunk < 1024)
+    p.chunk *= 2;
+  size_t entries = gqa::uniform_entries(*config, p.chunk);
+  if (gqa::scratch_bytes(*config, entries) > gqa::kNoAllocScratchBytes) return kErrWorkspace;   // batch * heads too large for 16 MiB
+  // whatever room is left lets the plan kernel use guided chunk sizes
+  while (entries < gqa::guided_entries(*config, p.chunk) && gqa::scratch_bytes(*config, entries + 64) <= gqa::kNoAllocScratchBytes) entries += 64;
+  p.capacity = int(entries);
   void* scratch = nullptr;
   if (int rc = gqa::noalloc_setup(device, &scratch)) return rc;
-  p.part_o = static_cast<float*>(scratch);
-  p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.hq * gqa::kD;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
-  gqa::gqa_decode_kernel<<<dim3(p.max_splits, (p.hkv + gqa::kWarps - 1) / gqa::kWarps, p.batch), gqa::kWarps * 32, gqa::kSmemBytes, s>>>(p);
-  gqa::gqa_reduce_kernel<<<dim3(p.hq, p.batch), gqa::kD, 0, s>>>(p);
-  return int(cudaGetLastError());
+  gqa::carve_scratch(p, static_cast<uint8_t*>(scratch));
+  int sms = 0;
+  if (int rc = gqa_sm_count(device, &sms)) return rc;
+  return gqa::launch(p, sms, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
