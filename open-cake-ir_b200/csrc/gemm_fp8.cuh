@@ -46,10 +46,13 @@ constexpr int kStageBytes = kBytesA + kBytesB;
 constexpr int kControlWarps = 4;                  // one warpgroup: warp 0 TMA, warp 1 MMA, warps 2-3 idle
 constexpr int kEpilogueWarps = 8;                 // two warpgroups: 2 column groups x 4 TMEM lane quadrants
 constexpr int kThreads = (kControlWarps + kEpilogueWarps) * 32;
-// Register budget moved between the warpgroups once the roles split (the kernel is launched with
-// 65536 / 384 -> 168 registers per thread): 128 control threads x 40 + 256 epilogue threads x 232 <= 65536.
+// Register budget moved between the warpgroups once the roles split.  The pool setmaxnreg draws on
+// is what the launch allocated, 168 registers x 384 threads = 64512, not the SM's 65536: an
+// increase that asks for more than the pool ever holds blocks for good.  128 x 40 + 256 x 232 = 64512.
 constexpr int kControlRegs = 40;
 constexpr int kEpilogueRegs = 232;
+static_assert(kControlWarps * 32 * kControlRegs + kEpilogueWarps * 32 * kEpilogueRegs <= (65536 / kThreads / 8 * 8) * kThreads,
+              "setmaxnreg budget exceeds the registers the launch allocates");
 constexpr int kMaxGroups = 512;
 
 enum Mode : int {
