@@ -70,16 +70,6 @@ __device__ __forceinline__ int seq_len(const Params& p, int b) {
 // K and V are read exactly once: their lines are marked evict-first in L2, and the partial
 // results evict-last, so that the stream does not push the partial results out to DRAM before
 // they are merged.
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t policy;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-  return policy;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t policy;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
-  return policy;
-}
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid, uint64_t policy) {
   const int bytes = valid ? 16 : 0;     // 0 source bytes = zero fill
   asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(bytes), "l"(policy)

@@ -6,20 +6,24 @@
 // out = bf16(softmax(logits) ckv), lse base 2.
 //
 // At 128 heads the operator does 242 flop per byte of latent cache, which is the bf16 ridge of the
-// machine, so both contractions run on the tensor core.  A CTA owns (128 heads, one half of the 512
-// output dims, sequence, KV chunk); the two halves of a chunk are neighbouring CTAs, so the second
-// reads the latent rows from L2.  The 128 heads are the 128 TMEM lanes:
-//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q and the tile K-major in shared memory
-//   O[128 x 256 dims]  += P[128 x 32] . V[32 x 256]     P from tensor memory, V = the same tile read
+// machine, so both contractions run on the tensor core.  A CTA owns (128 heads, one QUARTER of the
+// 512 output dims, sequence, KV chunk); the four quarters of a chunk are neighbouring CTAs, so three
+// of them read the latent rows from L2.  The 128 heads are the 128 TMEM lanes:
+//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q from TENSOR memory, the tile K-major in shared memory
+//   O[128 x 128 dims]  += P[128 x 32] . V[32 x 128]     P from tensor memory, V = the same tile read
 //                                                        MN-major (no transposed copy is made)
-// Q (147 KiB, nine 64-column slabs of 128-byte rows, 128-byte swizzle) stays in shared memory for
-// the whole CTA (its size is what limits the ring to two stages); 32-token tiles stream through a
-// two-stage cp.async ring in the same slab layout
-// (the gather is per token, so any page size works).  Four softmax warps own one head row each per
-// thread: they read S from TMEM, keep the running max and sum in base 2, and write P back to TMEM
-// as TWO bf16 terms (value + rounding residual; one term is not accurate enough for the
-// contract's tolerance).  The running max only moves when it grows by more than 2^8, so O is
-// rescaled in TMEM rarely.  Every wait is bounded and reports through the status word.
+// Q lives in tensor memory for the whole CTA (288 columns: 576 bf16 per lane), next to O (128
+// columns), S (32) and P (32).  Kept in shared memory it would take 147 KiB, leave room for two
+// ring stages only, and be re-read by every QK (1152 clocks of shared-memory bandwidth per tile);
+// in tensor memory it costs no shared-memory bandwidth and the whole 227 KiB becomes a six-stage
+// ring of 32-token tiles (cp.async gather per token, so any page size works; four tiles in
+// flight).  The price is that QK is computed by each of the four dim-quarter CTAs.  Four softmax
+// warps own one head row each per thread: they read S from TMEM, keep the running max and sum in
+// base 2, and write P back to TMEM as TWO bf16 terms (value + rounding residual; one term is not
+// accurate enough for the contract's tolerance).  The MMA warp issues QK of the next tile before
+// PV of the current one, so the tensor pipe works on QK while the softmax of the current tile
+// runs.  The running max only moves when it grows by more than 2^8, so O is rescaled in TMEM
+// rarely.  Every wait is bounded and reports through the status word.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <new>
@@ -31,21 +35,23 @@ constexpr int kCkv = 512, kKpe = 64, kRow = kCkv + kKpe;   // 576 elements per l
 constexpr int kSlabs = kRow / 64;                          // 9 slabs of 64 columns (128 bytes per row)
 constexpr int kRowChunks = kRow / 8;                       // 72 16-byte chunks per row
 constexpr int kHeads = 128;                                // query heads per CTA = TMEM lanes
-constexpr int kDimsPerCta = 256;                           // output dims per CTA (half of ckv)
+constexpr int kDimsPerCta = 128;                           // output dims per CTA (a quarter of ckv)
+constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, sequence, chunk)
 constexpr int kTile = 32;                                  // tokens per tile
-constexpr int kStages = 2;
-constexpr int kQSlabBytes = kHeads * 128;                  // 16 KiB
-constexpr int kQBytes = kSlabs * kQSlabBytes;              // 147 456
+constexpr int kStages = 6;                                 // ring stages
+constexpr int kInFlight = 4;                               // tiles a loader thread keeps in flight
 constexpr int kKvSlabBytes = kTile * 128;                  // 4 KiB
 constexpr int kKvStageBytes = kSlabs * kKvSlabBytes;       // 36 864
-constexpr int kLoaderWarps = 2, kLoaderThreads = kLoaderWarps * 32;
-constexpr int kMmaWarp = 2;
-constexpr int kSoftmaxWarp0 = 4;                           // warps 4..7: warp % 4 = TMEM lane quadrant
-constexpr int kThreads = 256;
+constexpr int kLoaderWarps = 4, kLoaderThreads = kLoaderWarps * 32;   // warps 0..3: eight rows of a tile each
+constexpr int kMmaWarp = 4;                                // warps 5..7 only take part in the CTA-wide barriers
+constexpr int kSoftmaxWarp0 = 8;                           // warps 8..15: warp % 4 = TMEM lane quadrant,
+constexpr int kSoftmaxWarps = 8;                           //   (warp - 8) / 4 = which 16 tokens of a tile
+constexpr int kThreads = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;                   // log2 units
-// tensor-memory columns
-constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kTmemColumns = 512;
+// tensor-memory columns: O fp32, S fp32, P as two bf16 terms (16 + 16 columns), Q bf16 (2 per column)
+constexpr uint32_t kColO = 0, kColS = 128, kColP = 160, kColQ = 192, kTmemColumns = 512;
+static_assert(kColQ + kRow / 2 <= kTmemColumns, "Q does not fit in tensor memory");
 
 struct Params {
   const __nv_bfloat16 *q_nope, *q_pe, *ckv, *kpe;
@@ -61,12 +67,15 @@ struct Params {
 
 struct Shared {
   uint64_t kv_full[kStages], kv_empty[kStages];
-  uint64_t s_full[2], s_free[2], p_ready[2], pv_done[2];
+  uint64_t s_full, s_free, p_ready, pv_done;      // one S and one P buffer: the tensor pipe is in order
+  uint64_t row_sums;                              // the two softmax warps of a row exchange their sums once
+  uint64_t q_moved;                               // Q has left its staging area (ring stages 2..5)
   uint32_t tmem_base;
   int abort_flag;
+  float l_part[2][kHeads];
 };
 
-constexpr size_t kSmemBytes = size_t(kQBytes) + kStages * kKvStageBytes + sizeof(Shared) + 1024;
+constexpr size_t kSmemBytes = size_t(kStages) * kKvStageBytes + sizeof(Shared) + 1024;
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
@@ -86,50 +95,51 @@ __device__ __forceinline__ uint32_t slab_off(int rows, int row, int chunk) {
   return uint32_t((chunk >> 3) * rows * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// One 32-token tile of latent rows -> one ring stage, by the two loader warps.  A warp takes 16
-// rows; its lanes cover consecutive 16-byte chunks of one row at a time (coalesced 512-byte reads),
-// and the page of each row is looked up once per tile by one lane and passed round by shuffle.
-__device__ __forceinline__ void load_tile(const Params& p, int b, int tok0, int len, uint32_t dst, int loader_tid) {
+// One 32-token tile of latent rows -> one ring stage, by the four loader warps.  A warp takes
+// eight rows; its lanes cover consecutive 16-byte chunks of one row at a time (coalesced 512-byte
+// reads).  The page of each row is looked up by one lane (`lookup_row`, issued a tile ahead so
+// that the dependent load of the page table is never waited for) and passed round by shuffle.
+__device__ __forceinline__ long long lookup_row(const Params& p, int page_base, int tok0, int len, int loader_tid) {
+  const int tok = tok0 + (loader_tid >> 5) * 8 + (loader_tid & 7);
+  if (tok >= len) return -1;
+  const int page = __ldg(p.kv_indices + page_base + tok / p.page_size);
+  return (long long)page * p.page_size + (tok % p.page_size);
+}
+__device__ __forceinline__ void load_tile(const Params& p, long long my_slot, uint32_t dst, int loader_tid) {
   const int w = loader_tid >> 5, lane = loader_tid & 31;
-  const int my_tok = tok0 + w * 16 + (lane & 15);
-  const bool my_valid = my_tok < len;
-  const int t = my_valid ? my_tok : 0;
-  const int page = __ldg(p.kv_indices + p.kv_indptr[b] + t / p.page_size);
-  const long long my_slot = (long long)page * p.page_size + (t % p.page_size);
 #pragma unroll
-  for (int rr = 0; rr < 16; ++rr) {
-    const int row = w * 16 + rr;
+  for (int rr = 0; rr < 8; ++rr) {
+    const int row = w * 8 + rr;
     const long long slot = __shfl_sync(0xffffffffu, my_slot, rr);
-    const bool valid = __shfl_sync(0xffffffffu, int(my_valid), rr) != 0;
-    const __nv_bfloat16* ckv_row = p.ckv + slot * kCkv;
+    const bool valid = slot >= 0;
+    const __nv_bfloat16* ckv_row = p.ckv + (valid ? slot : 0) * kCkv;
     cp_async_16(dst + slab_off(kTile, row, lane), ckv_row + lane * 8, valid);
     cp_async_16(dst + slab_off(kTile, row, 32 + lane), ckv_row + (32 + lane) * 8, valid);
-    if (lane < kKpe / 8) cp_async_16(dst + slab_off(kTile, row, kCkv / 8 + lane), p.kpe + slot * kKpe + lane * 8, valid);
+    if (lane < kKpe / 8) cp_async_16(dst + slab_off(kTile, row, kCkv / 8 + lane), p.kpe + (valid ? slot : 0) * kKpe + lane * 8, valid);
   }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
 mla_decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
-  const int dh = blockIdx.x & 1, hb = blockIdx.x >> 1, split = blockIdx.y, b = blockIdx.z;
+  const int dq = blockIdx.x % kDimSplit, hb = blockIdx.x / kDimSplit, split = blockIdx.y, b = blockIdx.z;
   const int len = seq_len(p, b);
   const int begin = split * p.chunk;
   if (begin >= len) return;
   const int end = min(len, begin + p.chunk);
   const int tiles = (end - begin + kTile - 1) / kTile;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t q_addr = smem_u32(base);
-  const uint32_t kv_addr = q_addr + kQBytes;
-  Shared* sh = reinterpret_cast<Shared*>(base + kQBytes + kStages * kKvStageBytes);
+  const uint32_t kv_addr = smem_u32(base);
+  Shared* sh = reinterpret_cast<Shared*>(base + kStages * kKvStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head0 = hb * kHeads;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->kv_full[s], kLoaderThreads); mbar_init(&sh->kv_empty[s], 1); }
-    for (int j = 0; j < 2; ++j) {
-      mbar_init(&sh->s_full[j], 1); mbar_init(&sh->s_free[j], 4);
-      mbar_init(&sh->p_ready[j], 4); mbar_init(&sh->pv_done[j], 1);
-    }
+    mbar_init(&sh->s_full, 1); mbar_init(&sh->s_free, kSoftmaxWarps);
+    mbar_init(&sh->p_ready, kSoftmaxWarps); mbar_init(&sh->pv_done, 1);
+    mbar_init(&sh->row_sums, kSoftmaxWarps);
+    mbar_init(&sh->q_moved, kSoftmaxWarps);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -137,19 +147,26 @@ mla_decode_kernel(const Params p) {
     tmem_alloc(&sh->tmem_base, kTmemColumns);
     tmem_relinquish();
   }
-  // the loader warps start the first tile before anything else so that it travels with the Q block
-  if (warp < kLoaderWarps) load_tile(p, b, begin, end, kv_addr, threadIdx.x);
-  // Q block -> shared memory, slab-major and swizzled like a TMA box would leave it
+  // Q block -> staging area in ring stages 2..5 (exactly 128 rows x 1152 bytes), coalesced; the
+  // 16-byte chunk index is XORed with the row's low bits so that a thread reading its own row
+  // later meets no bank conflicts.  From there each softmax thread moves its row to tensor memory.
+  const uint32_t q_stage = kv_addr + 2 * kKvStageBytes;
+  static_assert(4 * kKvStageBytes == kHeads * kRow * 2, "Q staging area = four ring stages");
   for (int idx = threadIdx.x; idx < kHeads * kRowChunks; idx += kThreads) {
     const int r = idx / kRowChunks, chunk = idx % kRowChunks;
     const int head = head0 + r;
     const bool valid = head < p.heads;
     const size_t hrow = size_t(b) * p.heads + (valid ? head : 0);
     const __nv_bfloat16* src = chunk < kCkv / 8 ? p.q_nope + hrow * kCkv + chunk * 8 : p.q_pe + hrow * kKpe + (chunk - kCkv / 8) * 8;
-    cp_async_16(q_addr + slab_off(kHeads, r, chunk), src, valid);
+    cp_async_16(q_stage + r * (kRow * 2) + ((chunk ^ (r & 7)) << 4), src, valid);
   }
   cp_async_commit();
-  cp_async_wait<0>();
+  // The first tile goes out while the Q block is in flight (its page lookup is two dependent loads);
+  // it is a copy group of its own, so that the barrier below waits for Q only.
+  const int page_base = p.kv_indptr[b];
+  if (warp < kLoaderWarps) load_tile(p, lookup_row(p, page_base, begin, end, threadIdx.x), kv_addr, threadIdx.x);
+  cp_async_commit();
+  cp_async_wait<1>();
   fence_proxy_async_smem();
   tcgen05_fence_before();
   __syncthreads();
@@ -159,18 +176,27 @@ mla_decode_kernel(const Params p) {
 
   if (warp < kLoaderWarps) {
     // ------------------------------ loader --------------------------------------------
+    // Up to kInFlight tiles of copies are outstanding per thread; a stage is announced when the
+    // thread's copies of that tile have landed.
     bool ok = true;
-    for (int i = 0; ok && i < tiles; ++i) {
-      const int s = i % kStages;
-      ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
-      if (!ok) break;
-      if (i > 0) {               // tile 0 was issued, and has landed, with the Q block
-        load_tile(p, b, begin + i * kTile, end, kv_addr + s * kKvStageBytes, threadIdx.x);
-        cp_async_commit();
-        cp_async_wait<0>();
+    long long my_slot = tiles > 1 ? lookup_row(p, page_base, begin + kTile, end, threadIdx.x) : -1;
+    for (int i = 0; ok && i < tiles + kInFlight - 1; ++i) {
+      if (i > 0 && i < tiles) {  // tile 0 went out before the CTA's barrier, as a copy group of its own
+        const int s = i % kStages;
+        const long long next_slot = i + 1 < tiles ? lookup_row(p, page_base, begin + (i + 1) * kTile, end, threadIdx.x) : -1;
+        ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
+        // stages 2..5 hold the Q block until the softmax warps have moved it to tensor memory
+        if (ok && i == 2) ok = mbar_wait(&sh->q_moved, 0, abort_flag, p.status, kStatusWaitFlag);
+        if (!ok) break;
+        load_tile(p, my_slot, kv_addr + s * kKvStageBytes, threadIdx.x);
+        my_slot = next_slot;
       }
-      fence_proxy_async_smem();
-      mbar_arrive(&sh->kv_full[s]);
+      if (i > 0) cp_async_commit();
+      if (i >= kInFlight - 1) {
+        cp_async_wait<kInFlight - 1>();
+        fence_proxy_async_smem();
+        mbar_arrive(&sh->kv_full[(i - (kInFlight - 1)) % kStages]);
+      }
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ----------------------------------------
@@ -178,87 +204,126 @@ mla_decode_kernel(const Params p) {
       constexpr uint32_t idesc_qk = umma_idesc_ex(1 /* bf16 */, kHeads, kTile, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_ex(1 /* bf16 */, kHeads, kDimsPerCta, 0, 1 /* V is MN-major */);
       bool ok = true;
-      for (int i = 0; ok && i <= tiles; ++i) {
-        // PV of the previous tile goes first: it is what releases that tile's ring stage, and with
-        // two stages the loader needs it back before it can fetch tile i+1.
-        if (i >= 1) {             // O += P(i-1) . V(i-1), P as two bf16 terms
-          const int t = i - 1, s = t % kStages, j = t & 1;
-          ok = mbar_wait(&sh->p_ready[j], (t >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
-          if (!ok) break;
-          tcgen05_fence_after();
-          const uint32_t v_addr = kv_addr + s * kKvStageBytes + dh * (kDimsPerCta / 64) * kKvSlabBytes;
+      // S(i) = Q . tile(i)^T, Q from tensor memory: 36 steps of 16 elements, 8 columns of Q each
+      auto issue_qk = [&](int i) {
+        const int s = i % kStages;
+        ok = mbar_wait(&sh->kv_full[s], (i / kStages) & 1, abort_flag, p.status, kStatusWaitSmemFull);
+        // S is free once the softmax warps have read tile i-1's logits (for i = 0: once Q is in place)
+        ok = ok && mbar_wait(&sh->s_free, i & 1, abort_flag, p.status, kStatusWaitTmemEmpty);
+        if (!ok) return;
+        tcgen05_fence_after();
+        // One descriptor per tile; the 36 steps differ by constants in its 16-byte address field
+        // (a slab further every four steps, 32 bytes inside the swizzled row otherwise), so the
+        // single issuing thread spends a few instructions per MMA, not a descriptor build.
+        const uint64_t b_base = umma_desc_sw128(kv_addr + s * kKvStageBytes);
 #pragma unroll
-          for (int term = 0; term < 2; ++term) {
-#pragma unroll
-            for (int ks = 0; ks < kTile / 16; ++ks) {
-              const uint32_t a_tmem = tmem_base + kColP + j * kTile + term * (kTile / 2) + ks * 8;
-              // 16 tokens = two 8-row groups of 1024 bytes; the next 64 dims are one slab further
-              const uint64_t b_desc = umma_desc_sw128_ex(v_addr + ks * 2048, kKvSlabBytes, 1024);
-              umma_f16_a_tmem(tmem_base + kColO, a_tmem, b_desc, idesc_pv, (t | term | ks) != 0);
-            }
-          }
-          tcgen05_commit(&sh->pv_done[j]);
-          tcgen05_commit(&sh->kv_empty[s]);
+        for (int step = 0; step < kRow / 16; ++step) {
+          const uint64_t b_desc = b_base + uint64_t(((step >> 2) * kKvSlabBytes + (step & 3) * 32) >> 4);
+          umma_f16_a_tmem(tmem_base + kColS, tmem_base + kColQ + step * 8, b_desc, idesc_qk, step != 0);
         }
-        if (i < tiles) {          // S(i) = Q . tile(i)^T
-          const int s = i % kStages, j = i & 1;
-          ok = mbar_wait(&sh->kv_full[s], (i / kStages) & 1, abort_flag, p.status, kStatusWaitSmemFull) &&
-               mbar_wait(&sh->s_free[j], ((i >> 1) & 1) ^ 1, abort_flag, p.status, kStatusWaitTmemEmpty);
-          if (!ok) break;
-          tcgen05_fence_after();
-          const uint32_t tile_addr = kv_addr + s * kKvStageBytes;
-#pragma unroll 1
-          for (int slab = 0; slab < kSlabs; ++slab) {
+        tcgen05_commit(&sh->s_full);
+      };
+      issue_qk(0);
+      for (int i = 0; ok && i < tiles; ++i) {
+        // QK of the next tile first: the tensor pipe works on it while the softmax of tile i runs
+        if (i + 1 < tiles) issue_qk(i + 1);
+        if (!ok) break;
+        // O += P(i) . V(i), P as two bf16 terms
+        const int s = i % kStages;
+        ok = mbar_wait(&sh->p_ready, i & 1, abort_flag, p.status, kStatusWaitFlag);
+        if (!ok) break;
+        tcgen05_fence_after();
+        // 16 tokens = two 8-row groups of 1024 bytes; the next 64 dims are one slab further
+        const uint64_t v_base = umma_desc_sw128_ex(kv_addr + s * kKvStageBytes + dq * (kDimsPerCta / 64) * kKvSlabBytes, kKvSlabBytes, 1024);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t a_desc = umma_desc_sw128(q_addr + slab * kQSlabBytes + kk * 32);
-              const uint64_t b_desc = umma_desc_sw128(tile_addr + slab * kKvSlabBytes + kk * 32);
-              umma_f16(tmem_base + kColS + j * kTile, a_desc, b_desc, idesc_qk, (slab | kk) != 0);
-            }
+        for (int term = 0; term < 2; ++term) {
+#pragma unroll
+          for (int ks = 0; ks < kTile / 16; ++ks) {
+            const uint32_t a_tmem = tmem_base + kColP + term * (kTile / 2) + ks * 8;
+            umma_f16_a_tmem(tmem_base + kColO, a_tmem, v_base + uint64_t((ks * 2048) >> 4), idesc_pv, (i | term | ks) != 0);
           }
-          tcgen05_commit(&sh->s_full[j]);
         }
+        tcgen05_commit(&sh->pv_done);
+        tcgen05_commit(&sh->kv_empty[s]);
       }
     }
   } else if (warp >= kSoftmaxWarp0) {
     // ------------------------------ softmax / epilogue --------------------------------
+    // Two warps per head row: both read the tile's 32 logits and agree on the running maximum;
+    // warp group g exponentiates tokens 16g..16g+15, keeps the sum over them, and owns half of
+    // the O columns when O is rescaled or written out.
     const int quad = warp & 3;
+    const int grp = (warp - kSoftmaxWarp0) >> 2;
     const int r = quad * 32 + lane;                 // head row of this thread
     const uint32_t lane_base = tmem_base + (uint32_t(quad * 32) << 16);
     const float scale2 = __ldg(p.sm_scale) * kLog2e;
-    float m_ref = -INFINITY, l = 0.f;
+    constexpr int kOwnCols = kDimsPerCta / 2;       // O columns per warp group
     bool ok = true;
+    {
+      // Q rows, staging area -> tensor memory: 576 bf16 = 288 columns, two elements per column, in the
+      // order of the latent row (512 q_nope, 64 q_pe); group 0 stores columns 0..159, group 1 the
+      // rest.  Heads past the end are rows of zeros.
+#pragma unroll 1
+      for (int c = grp * 160; c < (grp == 0 ? 160 : kRow / 2); c += 32) {       // 32 columns = 8 x 16 bytes per store
+        uint32_t w[32];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int chunk = c / 4 + k;                // 16-byte chunk of the 1152-byte row
+          const uint4 x = *reinterpret_cast<const uint4*>(base + 2 * kKvStageBytes + r * (kRow * 2) + ((chunk ^ (r & 7)) << 4));
+          w[4 * k] = x.x; w[4 * k + 1] = x.y; w[4 * k + 2] = x.z; w[4 * k + 3] = x.w;
+        }
+        tmem_st_32x32b_x32(lane_base + kColQ + c, reinterpret_cast<const float*>(w));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->q_moved);     // the staging area has been read
+      tcgen05_wait_st();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->s_free);      // phase 0 of s_free: Q is in place
+    }
+    float m_ref = -INFINITY, l = 0.f;               // l: this group's share of the row sum
     for (int i = 0; ok && i < tiles; ++i) {
-      const int j = i & 1;
-      ok = mbar_wait(&sh->s_full[j], (i >> 1) & 1, abort_flag, p.status, kStatusWaitTmemFull);
+      ok = mbar_wait(&sh->s_full, i & 1, abort_flag, p.status, kStatusWaitTmemFull);
       if (!ok) break;
       tcgen05_fence_after();
       float sc[kTile];
-      tmem_ld_32x32b_x32(lane_base + kColS + j * kTile, sc);
+      tmem_ld_32x32b_x32(lane_base + kColS, sc);
       tcgen05_wait_ld();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->s_free[j]);
+      if (lane == 0) mbar_arrive(&sh->s_free);      // phase i+1: S may be overwritten by QK(i+1)
+      // The softmax of a tile sits between QK(i) and PV(i): four-way partial maxima and sums keep
+      // its dependent chains short.
       const int tok0 = begin + i * kTile;
-      float tmax = -INFINITY;
+      float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (tok0 + kTile <= end) {                     // all but a chunk's last tile
 #pragma unroll
-      for (int c = 0; c < kTile; ++c) {
-        sc[c] = tok0 + c < end ? sc[c] * scale2 : -INFINITY;
-        tmax = fmaxf(tmax, sc[c]);
+        for (int c = 0; c < kTile; ++c) {
+          sc[c] *= scale2;
+          t4[c & 3] = fmaxf(t4[c & 3], sc[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kTile; ++c) {
+          sc[c] = tok0 + c < end ? sc[c] * scale2 : -INFINITY;
+          t4[c & 3] = fmaxf(t4[c & 3], sc[c]);
+        }
+      }
+      const float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
+      if (i > 0) {               // P, and O for a rescale, are free once PV(i-1) has completed
+        ok = mbar_wait(&sh->pv_done, (i - 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+        if (!ok) break;
+        tcgen05_fence_after();
       }
       if (i == 0) {
         m_ref = tmax;                                // finite: the first tile holds a valid token
       } else {
         const bool need = tmax > m_ref + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          // O is about to be rescaled in tensor memory: the PV of the previous tile must have landed
-          ok = mbar_wait(&sh->pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
-          if (!ok) break;
-          tcgen05_fence_after();
+        if (__any_sync(0xffffffffu, need)) {         // both warps of a row see the same logits and decide alike
           const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
           if (need) { m_ref = tmax; l *= alpha; }
 #pragma unroll 1
-          for (int c = 0; c < kDimsPerCta; c += 32) {
+          for (int c = grp * kOwnCols; c < (grp + 1) * kOwnCols; c += 32) {
             float o[32];
             tmem_ld_32x32b_x32(lane_base + kColO + c, o);
             tcgen05_wait_ld();
@@ -269,35 +334,40 @@ mla_decode_kernel(const Params p) {
           tcgen05_wait_st();
         }
       }
-      if (i >= 2) {              // the P buffer is free once the PV that read it has completed
-        ok = mbar_wait(&sh->pv_done[j], ((i - 2) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
-        if (!ok) break;
-      }
-      uint32_t hi[kTile / 2], lo[kTile / 2];
-      float sum = 0.f;
+      uint32_t hi[kTile / 4], lo[kTile / 4];
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < kTile; c += 2) {
-        const float p0 = exp2f(sc[c] - m_ref), p1 = exp2f(sc[c + 1] - m_ref);
-        sum += p0 + p1;
+      for (int c = 0; c < kTile / 2; c += 2) {
+        const float x0 = grp == 0 ? sc[c] : sc[kTile / 2 + c], x1 = grp == 0 ? sc[c + 1] : sc[kTile / 2 + c + 1];
+        const float p0 = exp2f(x0 - m_ref), p1 = exp2f(x1 - m_ref);
+        s4[(c >> 1) & 3] += p0 + p1;
         split_bf16x2(p0, p1, hi[c >> 1], lo[c >> 1]);
       }
-      l += sum;
-      tmem_st_32x32b_x16(lane_base + kColP + j * kTile, hi);
-      tmem_st_32x32b_x16(lane_base + kColP + j * kTile + kTile / 2, lo);
+      l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      tmem_st_32x32b_x8(lane_base + kColP + grp * (kTile / 4), hi);
+      tmem_st_32x32b_x8(lane_base + kColP + kTile / 2 + grp * (kTile / 4), lo);
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_ready[j]);
+      if (lane == 0) mbar_arrive(&sh->p_ready);
     }
-    if (ok) ok = mbar_wait(&sh->pv_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+    // the row sum is the two groups' sums; exchanged once through shared memory
+    if (ok) {
+      sh->l_part[grp][r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->row_sums);
+      ok = mbar_wait(&sh->row_sums, 0, abort_flag, p.status, kStatusWaitFlag);
+    }
+    if (ok) ok = mbar_wait(&sh->pv_done, (tiles - 1) & 1, abort_flag, p.status, kStatusWaitFlag);
     if (ok) {
       tcgen05_fence_after();
       const int head = head0 + r;
-      const float inv = 1.f / l;
+      const float total = sh->l_part[0][r] + sh->l_part[1][r];
+      const float inv = 1.f / total;
       const size_t slot = (size_t(b) * p.max_splits + split) * p.heads + (head < p.heads ? head : 0);
-      float* dst = p.part_o + slot * kCkv + dh * kDimsPerCta;
+      float* dst = p.part_o + slot * kCkv + dq * kDimsPerCta;
 #pragma unroll 1
-      for (int c = 0; c < kDimsPerCta; c += 32) {
+      for (int c = grp * kOwnCols; c < (grp + 1) * kOwnCols; c += 32) {
         float o[32];
         tmem_ld_32x32b_x32(lane_base + kColO + c, o);
         tcgen05_wait_ld();
@@ -307,7 +377,7 @@ mla_decode_kernel(const Params p) {
             *reinterpret_cast<float4*>(dst + c + k) = make_float4(o[k] * inv, o[k + 1] * inv, o[k + 2] * inv, o[k + 3] * inv);
         }
       }
-      if (dh == 0 && head < p.heads) p.part_lse[slot] = m_ref + log2f(l);
+      if (dq == 0 && grp == 0 && head < p.heads) p.part_lse[slot] = m_ref + log2f(total);
     }
   }
 
@@ -357,7 +427,7 @@ struct Handle {
 inline int pick_chunk(const cake_b200_mla_decode_config& c, int sms) {
   // Few, long chunks keep the partial-output traffic (heads * 512 fp32 per chunk) small next to
   // the latent rows a chunk reads (1152 B per token); enough of them to fill the SMs.
-  const long long head_blocks = 2LL * ((c.num_qo_heads + kHeads - 1) / kHeads);     // two dim halves per 128 heads
+  const long long head_blocks = (long long)kDimSplit * ((c.num_qo_heads + kHeads - 1) / kHeads);     // dim quarters per 128 heads
   const long long max_len = c.max_kv_len > 0 ? c.max_kv_len : 1;
   int chunk = 4096;
   while (chunk > 128 && c.batch * head_blocks * ((max_len * 5 / 8 + chunk - 1) / chunk) < 3LL * sms) chunk >>= 1;
@@ -432,7 +502,7 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
   CAKE_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), s));
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
-  mla::mla_decode_kernel<<<dim3(2 * head_blocks, p.max_splits, p.batch), mla::kThreads, mla::kSmemBytes, s>>>(p);
+  mla::mla_decode_kernel<<<dim3(mla::kDimSplit * head_blocks, p.max_splits, p.batch), mla::kThreads, mla::kSmemBytes, s>>>(p);
   mla::mla_reduce_kernel<<<dim3(p.heads, p.batch), 128, 0, s>>>(p);
   return int(cudaGetLastError());
 }
