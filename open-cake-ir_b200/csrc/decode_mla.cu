@@ -16,8 +16,8 @@
 // columns), S (32) and P (32).  Kept in shared memory it would take 147 KiB, leave room for two
 // ring stages only, and be re-read by every QK (1152 clocks of shared-memory bandwidth per tile);
 // in tensor memory it costs no shared-memory bandwidth and the whole 227 KiB becomes a six-stage
-// ring of 32-token tiles (cp.async gather per token, so any page size works; four tiles in
-// flight).  The price is that QK is computed by each of the four dim-quarter CTAs.  Four softmax
+// ring of 32-token tiles (cp.async gather per token, so any page size works; a stage's barrier
+// is arrived on by the copies themselves, so up to six tiles are in flight).  The price is that QK is computed by each of the four dim-quarter CTAs.  Four softmax
 // warps own one head row each per thread: they read S from TMEM, keep the running max and sum in
 // base 2, and write P back to TMEM as TWO bf16 terms (value + rounding residual; one term is not
 // accurate enough for the contract's tolerance).  The MMA warp issues QK of the next tile before
@@ -39,7 +39,6 @@ constexpr int kDimsPerCta = 128;                           // output dims per CT
 constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, sequence, chunk)
 constexpr int kTile = 32;                                  // tokens per tile
 constexpr int kStages = 6;                                 // ring stages
-constexpr int kInFlight = 4;                               // tiles a loader thread keeps in flight
 constexpr int kKvSlabBytes = kTile * 128;                  // 4 KiB
 constexpr int kKvStageBytes = kSlabs * kKvSlabBytes;       // 36 864
 constexpr int kLoaderWarps = 4, kLoaderThreads = kLoaderWarps * 32;   // warps 0..3: eight rows of a tile each
@@ -84,6 +83,10 @@ __device__ __forceinline__ int seq_len(const Params& p, int b) {
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;      // 0 source bytes = zero fill
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// Makes `bar` receive one (pre-counted) arrival from this thread once all its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -176,27 +179,22 @@ mla_decode_kernel(const Params p) {
 
   if (warp < kLoaderWarps) {
     // ------------------------------ loader --------------------------------------------
-    // Up to kInFlight tiles of copies are outstanding per thread; a stage is announced when the
-    // thread's copies of that tile have landed.
+    // A stage is announced by the copies themselves: each thread's arrival on the stage's barrier
+    // is tied to the completion of the copies it has just issued, so nothing here waits for data
+    // and as many tiles are in flight as the ring has free stages.
     bool ok = true;
     long long my_slot = tiles > 1 ? lookup_row(p, page_base, begin + kTile, end, threadIdx.x) : -1;
-    for (int i = 0; ok && i < tiles + kInFlight - 1; ++i) {
-      if (i > 0 && i < tiles) {  // tile 0 went out before the CTA's barrier, as a copy group of its own
-        const int s = i % kStages;
-        const long long next_slot = i + 1 < tiles ? lookup_row(p, page_base, begin + (i + 1) * kTile, end, threadIdx.x) : -1;
-        ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
-        // stages 2..5 hold the Q block until the softmax warps have moved it to tensor memory
-        if (ok && i == 2) ok = mbar_wait(&sh->q_moved, 0, abort_flag, p.status, kStatusWaitFlag);
-        if (!ok) break;
-        load_tile(p, my_slot, kv_addr + s * kKvStageBytes, threadIdx.x);
-        my_slot = next_slot;
-      }
-      if (i > 0) cp_async_commit();
-      if (i >= kInFlight - 1) {
-        cp_async_wait<kInFlight - 1>();
-        fence_proxy_async_smem();
-        mbar_arrive(&sh->kv_full[(i - (kInFlight - 1)) % kStages]);
-      }
+    cp_async_arrive_on(&sh->kv_full[0]);            // tile 0 went out before the CTA's barrier
+    for (int i = 1; ok && i < tiles; ++i) {
+      const int s = i % kStages;
+      const long long next_slot = i + 1 < tiles ? lookup_row(p, page_base, begin + (i + 1) * kTile, end, threadIdx.x) : -1;
+      ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
+      // stages 2..5 hold the Q block until the softmax warps have moved it to tensor memory
+      if (ok && i == 2) ok = mbar_wait(&sh->q_moved, 0, abort_flag, p.status, kStatusWaitFlag);
+      if (!ok) break;
+      load_tile(p, my_slot, kv_addr + s * kKvStageBytes, threadIdx.x);
+      cp_async_arrive_on(&sh->kv_full[s]);
+      my_slot = next_slot;
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ----------------------------------------
@@ -211,6 +209,7 @@ mla_decode_kernel(const Params p) {
         // S is free once the softmax warps have read tile i-1's logits (for i = 0: once Q is in place)
         ok = ok && mbar_wait(&sh->s_free, i & 1, abort_flag, p.status, kStatusWaitTmemEmpty);
         if (!ok) return;
+        fence_proxy_async_smem();               // the tile was written by cp.async (generic proxy), the MMA reads it through the async proxy
         tcgen05_fence_after();
         // One descriptor per tile; the 36 steps differ by constants in its 16-byte address field
         // (a slab further every four steps, 32 bytes inside the swizzled row otherwise), so the
