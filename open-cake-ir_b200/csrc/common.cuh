@@ -360,6 +360,35 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, float* v) {
       : "memory");
 }
 
+// Exclusive scan over the 1024 threads of a CTA (every thread must call); `total` receives the sum
+// and `warp_sums` is 32 elements of shared memory.
+template <typename T>
+__device__ __forceinline__ T cta1024_exclusive_scan(T value, T* warp_sums, T& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  T inc = value;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const T up = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += up;
+  }
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {                      // the 32 warp totals: inclusive scan in place
+    T w = warp_sums[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const T up = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += up;
+    }
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  total = warp_sums[31];
+  const T before = warp > 0 ? warp_sums[warp - 1] : T(0);
+  __syncthreads();                      // warp_sums may be reused by the next scan
+  return before + inc - value;
+}
+
 // ---- small numeric helpers ---------------------------------------------------------------
 // Two fp32 FMAs in one instruction (fma.rn.f32x2, new with sm_100): d = a * b + c element-wise.
 #ifndef CAKE_FMA_VARIANT

@@ -129,34 +129,6 @@ __device__ __forceinline__ void load_half(const __nv_bfloat16* __restrict__ cach
 __device__ __forceinline__ int item_begin(const int4& r) { return (r.y >> 11) * 64; }
 __device__ __forceinline__ int item_tokens(const int4& r) { return r.y & 2047; }
 
-// Exclusive scan over the 1024 threads of the plan CTA; `total` receives the sum.
-template <typename T>
-__device__ __forceinline__ T plan_scan(T value, T* warp_sums, T& total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  T inc = value;
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const T up = __shfl_up_sync(0xffffffffu, inc, d);
-    if (lane >= d) inc += up;
-  }
-  if (lane == 31) warp_sums[warp] = inc;
-  __syncthreads();
-  if (warp == 0) {                      // the 32 warp totals: inclusive scan in place
-    T w = warp_sums[lane];
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const T up = __shfl_up_sync(0xffffffffu, w, d);
-      if (lane >= d) w += up;
-    }
-    warp_sums[lane] = w;
-  }
-  __syncthreads();
-  total = warp_sums[31];
-  const T before = warp > 0 ? warp_sums[warp - 1] : T(0);
-  __syncthreads();                      // warp_sums may be reused by the next scan
-  return before + inc - value;
-}
-
 // Chunk size for a sequence that starts when `remaining` tokens (over all sequences, in list
 // order) are still to be listed.  Guided sizes: a fixed share of what is left per worker, between
 // kGuideMin tokens and the base chunk, in multiples of 64 -- full-size chunks first, smaller ones
@@ -185,7 +157,7 @@ gqa_plan_kernel(const Params p) {
   const int len0 = tid < p.batch ? seq_len(p, tid) : 0;              // the first 1024 lengths stay in registers
   long long mine = len0, all_tokens = 0;
   for (int b = tid + 1024; b < p.batch; b += 1024) mine += seq_len(p, b);
-  plan_scan(mine, sums64, all_tokens);
+  cta1024_exclusive_scan(mine, sums64, all_tokens);
 
   bool guided = true;
   for (int pass = 0; pass < 2; ++pass) {       // a second time only if the guided list does not fit
@@ -196,11 +168,11 @@ gqa_plan_kernel(const Params p) {
       const int len = base == 0 ? len0 : (b < p.batch ? seq_len(p, b) : 0);
       long long batch_tokens = len;
       long long start = tokens_before;
-      if (p.batch > 1024 || guided) start += plan_scan((long long)len, sums64, batch_tokens);
+      if (p.batch > 1024 || guided) start += cta1024_exclusive_scan((long long)len, sums64, batch_tokens);
       const int c = chunk_at(p, all_tokens - start, guided, share);
       const int n = (len + c - 1) / c;
       int batch_entries;
-      const int first = entries_before + plan_scan(n, sums32, batch_entries);
+      const int first = entries_before + cta1024_exclusive_scan(n, sums32, batch_entries);
       const bool fits = !guided || entries_before + batch_entries <= p.capacity;     // uniform for the CTA
       if (fits && b < p.batch) {
         // Entries written while a later batch turns out not to fit are simply written again.

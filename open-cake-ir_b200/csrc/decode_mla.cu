@@ -1,4 +1,4 @@
-// Paged MLA decode (absorbed form) for sm_100a: split-KV flash-decode on tcgen05 + reduce.
+// Paged MLA decode (absorbed form) for sm_100a: split-KV flash-decode on tcgen05 (plan + decode + reduce).
 //
 // Operator: src/open_cake_ir/tasks/solx_fib/attention.py:132-183, MLA branch (:164-165,
 // :175-177); tensor ABI attention_specs.py:249-292.  All query heads share one latent KV row of
@@ -6,9 +6,10 @@
 // out = bf16(softmax(logits) ckv), lse base 2.
 //
 // At 128 heads the operator does 242 flop per byte of latent cache, which is the bf16 ridge of the
-// machine, so both contractions run on the tensor core.  A CTA owns (128 heads, one QUARTER of the
-// 512 output dims, sequence, KV chunk); the four quarters of a chunk are neighbouring CTAs, so three
-// of them read the latent rows from L2.  The 128 heads are the 128 TMEM lanes:
+// machine, so both contractions run on the tensor core.  A CTA owns 128 heads, one QUARTER of the
+// 512 output dims and an equal share of all the tiles of the launch (a consecutive range of the
+// list of tiles of all sequences, so it works through one to a few sequences in turn); the four
+// quarters of a range are neighbouring CTAs, so three of them read the latent rows from L2.  The 128 heads are the 128 TMEM lanes:
 //   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q from TENSOR memory, the tile K-major in shared memory
 //   O[128 x 128 dims]  += P[128 x 32] . V[32 x 128]     P from tensor memory, V = the same tile read
 //                                                        MN-major (no transposed copy is made)
@@ -58,10 +59,11 @@ struct Params {
   const float* sm_scale;
   __nv_bfloat16* out;     // [B, H, 512]
   float* lse;             // [B, H]
-  float* part_o;          // [B, splits, H, 512]
-  float* part_lse;        // [B, splits, H]
+  float* part_o;          // [slots, H, 512]   slot = worker + sequence (see mla_plan_kernel)
+  float* part_lse;        // [slots, H]
+  int* tile_prefix;       // [B+1] 32-token tiles before sequence b, written by the plan kernel
   int* status;
-  int batch, heads, page_size, chunk, max_splits;
+  int batch, heads, page_size, workers;
 };
 
 struct Shared {
@@ -122,20 +124,67 @@ __device__ __forceinline__ void load_tile(const Params& p, long long my_slot, ui
   }
 }
 
+// The tiles of all sequences, in order, form one list; worker w (of `workers`) takes the w-th of
+// `workers` equal consecutive ranges of it, so every SM has the same number of tiles whatever the
+// lengths are, and a sequence is cut only where a range ends.  A (worker, sequence) pair that
+// meets writes one partial result; along the list both indices only grow, so worker + sequence
+// numbers the pairs uniquely and at most workers + batch - 1 slots are needed.
+__device__ __forceinline__ int tiles_per_worker(const Params& p) {
+  const int total = p.tile_prefix[p.batch];
+  return total > 0 ? (total + p.workers - 1) / p.workers : 1;
+}
+
+// One CTA: tile_prefix[b] = tiles before sequence b (exclusive scan), tile_prefix[B] = all tiles.
+__global__ void __launch_bounds__(1024)
+mla_plan_kernel(const Params p) {
+  __shared__ int sums[32];
+  if (threadIdx.x == 0) *p.status = 0;
+  int before = 0;
+  for (int base = 0; base < p.batch; base += 1024) {
+    const int b = base + threadIdx.x;
+    const int n = b < p.batch ? (seq_len(p, b) + kTile - 1) / kTile : 0;
+    int batch_total;
+    const int mine = before + cta1024_exclusive_scan(n, sums, batch_total);
+    if (b < p.batch) p.tile_prefix[b] = mine;
+    before += batch_total;
+  }
+  if (threadIdx.x == 0) p.tile_prefix[p.batch] = before;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 mla_decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
-  const int dq = blockIdx.x % kDimSplit, hb = blockIdx.x / kDimSplit, split = blockIdx.y, b = blockIdx.z;
-  const int len = seq_len(p, b);
-  const int begin = split * p.chunk;
-  if (begin >= len) return;
-  const int end = min(len, begin + p.chunk);
-  const int tiles = (end - begin + kTile - 1) / kTile;
+  const int head_blocks = (p.heads + kHeads - 1) / kHeads;
+  const int dq = blockIdx.x % kDimSplit, hb = (blockIdx.x / kDimSplit) % head_blocks, worker = blockIdx.x / (kDimSplit * head_blocks);
+  const int per_worker = tiles_per_worker(p);
+  const int range_begin = worker * per_worker, range_end = min(p.tile_prefix[p.batch], range_begin + per_worker);
+  if (range_begin >= range_end) return;            // the whole CTA leaves together
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t kv_addr = smem_u32(base);
   Shared* sh = reinterpret_cast<Shared*>(base + kStages * kKvStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head0 = hb * kHeads;
+  if (threadIdx.x == 0) sh->abort_flag = 0;
+  if (warp == kMmaWarp) {
+    tmem_alloc(&sh->tmem_base, kTmemColumns);
+    tmem_relinquish();
+  }
+
+  // One pass of the loop below per sequence this worker's range touches.
+  for (int at = range_begin; at < range_end;) {
+  int b = 0;
+  for (int lo = 0, hi = p.batch; hi - lo > 1;) {   // the sequence tile `at` belongs to: largest b with prefix[b] <= at
+    const int mid = (lo + hi) >> 1;
+    if (p.tile_prefix[mid] <= at) lo = mid; else hi = mid;
+    b = lo;
+  }
+  const int first_tile = at - p.tile_prefix[b];
+  const int tiles = min(p.tile_prefix[b + 1], range_end) - at;
+  at += tiles;
+  const int len = seq_len(p, b);
+  const int begin = first_tile * kTile;
+  const int end = min(len, begin + tiles * kTile);
+  const int slot_index = worker + b;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->kv_full[s], kLoaderThreads); mbar_init(&sh->kv_empty[s], 1); }
@@ -143,12 +192,7 @@ mla_decode_kernel(const Params p) {
     mbar_init(&sh->p_ready, kSoftmaxWarps); mbar_init(&sh->pv_done, 1);
     mbar_init(&sh->row_sums, kSoftmaxWarps);
     mbar_init(&sh->q_moved, kSoftmaxWarps);
-    sh->abort_flag = 0;
     fence_barrier_init();
-  }
-  if (warp == kMmaWarp) {
-    tmem_alloc(&sh->tmem_base, kTmemColumns);
-    tmem_relinquish();
   }
   // Q block -> staging area in ring stages 2..5 (exactly 128 rows x 1152 bytes), coalesced; the
   // 16-byte chunk index is XORed with the row's low bits so that a thread reading its own row
@@ -363,7 +407,7 @@ mla_decode_kernel(const Params p) {
       const int head = head0 + r;
       const float total = sh->l_part[0][r] + sh->l_part[1][r];
       const float inv = 1.f / total;
-      const size_t slot = (size_t(b) * p.max_splits + split) * p.heads + (head < p.heads ? head : 0);
+      const size_t slot = size_t(slot_index) * p.heads + (head < p.heads ? head : 0);
       float* dst = p.part_o + slot * kCkv + dq * kDimsPerCta;
 #pragma unroll 1
       for (int c = grp * kOwnCols; c < (grp + 1) * kOwnCols; c += 32) {
@@ -382,11 +426,11 @@ mla_decode_kernel(const Params p) {
 
   cp_async_wait<0>();
   tcgen05_fence_before();
-  __syncthreads();
-  if (warp == kMmaWarp) {
-    tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kTmemColumns);
+  __syncthreads();                                 // every role is done with this sequence's barriers and tiles
+  tcgen05_fence_after();
+  if (sh->abort_flag) break;
   }
+  if (warp == kMmaWarp) tmem_dealloc(sh->tmem_base, kTmemColumns);
 }
 
 // One CTA per (sequence, head): merges the chunks.  128 threads x 4 dims.
@@ -401,17 +445,19 @@ mla_reduce_kernel(const Params p) {
     if (threadIdx.x == 0) p.lse[size_t(b) * p.heads + head] = -INFINITY;
     return;
   }
-  const int splits = (len + p.chunk - 1) / p.chunk;
+  // the partial results of sequence b: one per worker whose range holds some of its tiles
+  const int per_worker = tiles_per_worker(p);
+  const int first_worker = p.tile_prefix[b] / per_worker, last_worker = (p.tile_prefix[b + 1] - 1) / per_worker;
   float mm = -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p.part_lse[(size_t(b) * p.max_splits + s) * p.heads + head]);
+  for (int w = first_worker; w <= last_worker; ++w) mm = fmaxf(mm, p.part_lse[size_t(w + b) * p.heads + head]);
   float total = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < splits; ++s) {
-    const size_t slot = (size_t(b) * p.max_splits + s) * p.heads + head;
-    const float w = exp2f(p.part_lse[slot] - mm);
+  for (int w = first_worker; w <= last_worker; ++w) {
+    const size_t slot = size_t(w + b) * p.heads + head;
+    const float wt = exp2f(p.part_lse[slot] - mm);
     const float4 v = *reinterpret_cast<const float4*>(p.part_o + slot * kCkv + d);
-    total += w;
-    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    total += wt;
+    acc.x += wt * v.x; acc.y += wt * v.y; acc.z += wt * v.z; acc.w += wt * v.w;
   }
   const float inv = 1.f / total;
   *reinterpret_cast<uint2*>(out) = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
@@ -423,15 +469,11 @@ struct Handle {
   Params p;
 };
 
-inline int pick_chunk(const cake_b200_mla_decode_config& c, int sms) {
-  // Few, long chunks keep the partial-output traffic (heads * 512 fp32 per chunk) small next to
-  // the latent rows a chunk reads (1152 B per token); enough of them to fill the SMs.
-  const long long head_blocks = (long long)kDimSplit * ((c.num_qo_heads + kHeads - 1) / kHeads);     // dim quarters per 128 heads
-  const long long max_len = c.max_kv_len > 0 ? c.max_kv_len : 1;
-  int chunk = 4096;
-  while (chunk > 128 && c.batch * head_blocks * ((max_len * 5 / 8 + chunk - 1) / chunk) < 3LL * sms) chunk >>= 1;
-  return chunk;
-}
+constexpr int kMaxWorkers = 64;                            // workers the scratch is sized for (SMs / 4 per head block)
+
+// Workspace behind the 256-byte status block: tile_prefix [B+1] int | part_o [slots, H, 512] f32 | part_lse [slots, H] f32
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+inline size_t slots_for(const cake_b200_mla_decode_config& c) { return size_t(kMaxWorkers) + size_t(c.batch); }
 
 }  // namespace mla
 }  // namespace cake
@@ -443,10 +485,9 @@ static bool mla_config_ok(const cake_b200_mla_decode_config& c) {
 
 extern "C" size_t cake_b200_mla_decode_workspace_bytes(const cake_b200_mla_decode_config* c) {
   if (!c || !mla_config_ok(*c)) return 0;
-  const int chunk = cake::mla::pick_chunk(*c, 148);
-  const size_t splits = size_t((c->max_kv_len + chunk - 1) / chunk) + 1;
-  const size_t slots = size_t(c->batch) * splits * c->num_qo_heads;
-  return 256 + slots * (cake::mla::kCkv + 1) * sizeof(float) + 256;
+  const size_t slots = cake::mla::slots_for(*c);
+  return 256 + cake::mla::align256((size_t(c->batch) + 1) * sizeof(int)) +
+         slots * c->num_qo_heads * (cake::mla::kCkv + 1) * sizeof(float) + 256;
 }
 
 extern "C" int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_decode_config* config, void** handle_out) {
@@ -477,12 +518,17 @@ extern "C" int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_d
   p.batch = int(config->batch);
   p.heads = config->num_qo_heads;
   p.page_size = config->page_size;
-  p.chunk = mla::pick_chunk(*config, 148);
-  p.max_splits = int((config->max_kv_len + p.chunk - 1) / p.chunk) + 1;
   p.status = static_cast<int*>(buffers[10]);
   uint8_t* ws = static_cast<uint8_t*>(buffers[10]) + 256;
+  p.tile_prefix = reinterpret_cast<int*>(ws);
+  ws += mla::align256((size_t(p.batch) + 1) * sizeof(int));
   p.part_o = reinterpret_cast<float*>(ws);
-  p.part_lse = p.part_o + size_t(p.batch) * p.max_splits * p.heads * mla::kCkv;
+  p.part_lse = p.part_o + mla::slots_for(*config) * p.heads * mla::kCkv;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) { delete h; return kErrBadArgument; }
+  const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
+  p.workers = sms / (mla::kDimSplit * head_blocks);          // one CTA per SM
+  p.workers = p.workers < 1 ? 1 : (p.workers > mla::kMaxWorkers ? mla::kMaxWorkers : p.workers);
   int rc = int(cudaFuncSetAttribute(mla::mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(mla::kSmemBytes)));
   if (rc) { delete h; return rc; }
   *handle_out = h;
@@ -499,9 +545,9 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   const mla::Params& p = h->p;
   if (p.batch == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
-  CAKE_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), s));
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
-  mla::mla_decode_kernel<<<dim3(mla::kDimSplit * head_blocks, p.max_splits, p.batch), mla::kThreads, mla::kSmemBytes, s>>>(p);
+  mla::mla_plan_kernel<<<1, 1024, 0, s>>>(p);
+  mla::mla_decode_kernel<<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
   mla::mla_reduce_kernel<<<dim3(p.heads, p.batch), 128, 0, s>>>(p);
   return int(cudaGetLastError());
 }
