@@ -206,7 +206,9 @@ size_t cake_b200_gqa_decode_noalloc_scratch_limit(void);
  * buffers: q_nope bf16 [B,H,512], q_pe bf16 [B,H,64], ckv_cache bf16 [pages,page_size,512],
  *          kpe_cache bf16 [pages,page_size,64], kv_indptr int32 [B+1], kv_indices int32 [*],
  *          kv_last_page_len int32 [B], sm_scale fp32 [1], output bf16 [B,H,512], lse fp32 [B,H], workspace.
- *          H % 16 == 0.
+ *          Any H (128 heads per CTA, the last block padded); batch <= 65535.  A launch is three kernels (tile
+ *          prefix, decode, merge of the partial results); the work is cut on the device from the sequence
+ *          lengths, so max_kv_len does not enter the workspace size.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   int64_t batch;
