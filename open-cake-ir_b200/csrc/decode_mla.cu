@@ -6,21 +6,24 @@
 // out = bf16(softmax(logits) ckv), lse base 2.
 //
 // At 128 heads the operator does 242 flop per byte of latent cache, which is the bf16 ridge of the
-// machine, so both contractions run on the tensor core.  A CTA owns 128 heads, one QUARTER of the
-// 512 output dims and an equal share of all the tiles of the launch (a consecutive range of the
-// list of tiles of all sequences, so it works through one to a few sequences in turn); the four
-// quarters of a range are neighbouring CTAs, so three of them read the latent rows from L2.  The 128 heads are the 128 TMEM lanes:
-//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q from TENSOR memory, the tile K-major in shared memory
-//   O[128 x 128 dims]  += P[128 x 32] . V[32 x 128]     P from tensor memory, V = the same tile read
+// machine, so both contractions run on the tensor core.  A CTA owns 128 heads, one HALF of the 512
+// output dims and an equal share of all the tiles of the launch (a consecutive range of the list
+// of tiles of all sequences, so it works through one to a few sequences in turn); the two halves
+// of a range are neighbouring CTAs, so one of them reads the latent rows from L2.  The 128 heads
+// are the 128 TMEM lanes:
+//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q dims 0..383 from TENSOR memory, 384..575 and
+//                                                        the tile K-major from shared memory
+//   O[128 x 256 dims]  += P[128 x 32] . V[32 x 256]     P from tensor memory, V = the same tile read
 //                                                        MN-major (no transposed copy is made)
-// Q lives in tensor memory for the whole CTA (288 columns: 576 bf16 per lane), next to O (128
-// columns), S (32) and P (32).  Kept in shared memory it would take 147 KiB, leave room for two
-// ring stages only, and be re-read by every QK (1152 clocks of shared-memory bandwidth per tile);
-// in tensor memory it costs no shared-memory bandwidth and the whole 227 KiB becomes a six-stage
-// ring of 32-token tiles (cp.async gather per token, so any page size works; a stage's barrier
-// is arrived on by the copies themselves, so up to six tiles are in flight).  The price is that QK is computed by each of the four dim-quarter CTAs.  Four softmax
-// warps own one head row each per thread: they read S from TMEM, keep the running max and sum in
-// base 2, and write P back to TMEM as TWO bf16 terms (value + rounding residual; one term is not
+// Tensor memory holds O (256 columns), S (32), P (32) and as much of Q as fits beside them (192
+// columns = 384 of a row's 576 bf16); the rest of Q (48 KiB) stays in shared memory.  All of Q in
+// shared memory would take 147 KiB, leave room for two ring stages only, and be re-read by every
+// QK (1152 clocks of shared-memory bandwidth per tile); all of Q in tensor memory leaves O only
+// 128 columns, i.e. four CTAs per range that each repeat the QK product AND the softmax.  With the
+// split, 179 KiB of shared memory are a four-stage ring of 32-token tiles (cp.async gather per
+// token, so any page size works; a stage's barrier is arrived on by the copies themselves).
+// Eight softmax warps, two per head row, read S from TMEM, keep the running max and sum in base
+// 2, and write P back to TMEM as TWO bf16 terms (value + rounding residual; one term is not
 // accurate enough for the contract's tolerance).  The MMA warp issues QK of the next tile before
 // PV of the current one, so the tensor pipe works on QK while the softmax of the current tile
 // runs.  The running max only moves when it grows by more than 2^8, so O is rescaled in TMEM
@@ -36,10 +39,16 @@ constexpr int kCkv = 512, kKpe = 64, kRow = kCkv + kKpe;   // 576 elements per l
 constexpr int kSlabs = kRow / 64;                          // 9 slabs of 64 columns (128 bytes per row)
 constexpr int kRowChunks = kRow / 8;                       // 72 16-byte chunks per row
 constexpr int kHeads = 128;                                // query heads per CTA = TMEM lanes
-constexpr int kDimsPerCta = 128;                           // output dims per CTA (a quarter of ckv)
-constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, sequence, chunk)
+constexpr int kDimsPerCta = 256;                           // output dims per CTA (half of ckv)
+constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, tile range)
+constexpr int kQTmemSlabs = 6;                             // Q dims 0..383 live in tensor memory,
+constexpr int kQSmemSlabs = kSlabs - kQTmemSlabs;          //   dims 384..575 (three slabs) in shared memory
+constexpr int kQTmemCols = kQTmemSlabs * 32;               // 192 columns, two bf16 per column
+constexpr int kQSlabBytes = kHeads * 128;                  // 16 KiB
+constexpr int kQSmemBytes = kQSmemSlabs * kQSlabBytes;     // 48 KiB
+constexpr int kQStageRow = kQTmemSlabs * 128;              // 768 bytes of a Q row pass through the staging area
 constexpr int kTile = 32;                                  // tokens per tile
-constexpr int kStages = 6;                                 // ring stages
+constexpr int kStages = 4;                                 // ring stages
 constexpr int kKvSlabBytes = kTile * 128;                  // 4 KiB
 constexpr int kKvStageBytes = kSlabs * kKvSlabBytes;       // 36 864
 constexpr int kLoaderWarps = 4, kLoaderThreads = kLoaderWarps * 32;   // warps 0..3: eight rows of a tile each
@@ -49,9 +58,9 @@ constexpr int kSoftmaxWarps = 8;                           //   (warp - 8) / 4 =
 constexpr int kThreads = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;                   // log2 units
-// tensor-memory columns: O fp32, S fp32, P as two bf16 terms (16 + 16 columns), Q bf16 (2 per column)
-constexpr uint32_t kColO = 0, kColS = 128, kColP = 160, kColQ = 192, kTmemColumns = 512;
-static_assert(kColQ + kRow / 2 <= kTmemColumns, "Q does not fit in tensor memory");
+// tensor-memory columns: O fp32 (256), S fp32 (32), P as two bf16 terms (16 + 16), Q dims 0..383 (192): all 512
+constexpr uint32_t kColO = 0, kColS = kColO + kDimsPerCta, kColP = kColS + kTile, kColQ = kColP + kTile, kTmemColumns = 512;
+static_assert(kColQ + kQTmemCols <= kTmemColumns, "Q does not fit in tensor memory");
 
 struct Params {
   const __nv_bfloat16 *q_nope, *q_pe, *ckv, *kpe;
@@ -70,13 +79,13 @@ struct Shared {
   uint64_t kv_full[kStages], kv_empty[kStages];
   uint64_t s_full, s_free, p_ready, pv_done;      // one S and one P buffer: the tensor pipe is in order
   uint64_t row_sums;                              // the two softmax warps of a row exchange their sums once
-  uint64_t q_moved;                               // Q has left its staging area (ring stages 2..5)
+  uint64_t q_moved;                               // Q has left its staging area (ring stages 1..3)
   uint32_t tmem_base;
   int abort_flag;
   float l_part[2][kHeads];
 };
 
-constexpr size_t kSmemBytes = size_t(kStages) * kKvStageBytes + sizeof(Shared) + 1024;
+constexpr size_t kSmemBytes = size_t(kQSmemBytes) + size_t(kStages) * kKvStageBytes + sizeof(Shared) + 1024;
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
@@ -160,8 +169,9 @@ mla_decode_kernel(const Params p) {
   const int range_begin = worker * per_worker, range_end = min(p.tile_prefix[p.batch], range_begin + per_worker);
   if (range_begin >= range_end) return;            // the whole CTA leaves together
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t kv_addr = smem_u32(base);
-  Shared* sh = reinterpret_cast<Shared*>(base + kStages * kKvStageBytes);
+  const uint32_t q_tail_addr = smem_u32(base);                      // Q dims 384..575, slab-major, 128-byte swizzle
+  const uint32_t kv_addr = q_tail_addr + kQSmemBytes;
+  Shared* sh = reinterpret_cast<Shared*>(base + kQSmemBytes + kStages * kKvStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head0 = hb * kHeads;
   if (threadIdx.x == 0) sh->abort_flag = 0;
@@ -194,18 +204,22 @@ mla_decode_kernel(const Params p) {
     mbar_init(&sh->q_moved, kSoftmaxWarps);
     fence_barrier_init();
   }
-  // Q block -> staging area in ring stages 2..5 (exactly 128 rows x 1152 bytes), coalesced; the
-  // 16-byte chunk index is XORed with the row's low bits so that a thread reading its own row
-  // later meets no bank conflicts.  From there each softmax thread moves its row to tensor memory.
-  const uint32_t q_stage = kv_addr + 2 * kKvStageBytes;
-  static_assert(4 * kKvStageBytes == kHeads * kRow * 2, "Q staging area = four ring stages");
+  // Q block, coalesced: the first 768 bytes of every row -> a staging area in ring stages 1..3 (the
+  // 16-byte chunk index XORed with the row's low bits, so that a thread reading its own row later
+  // meets no bank conflicts; from there each softmax thread moves its row to tensor memory); the
+  // last 384 bytes -> their final place, three K-major slabs laid out as a 128-byte-swizzled TMA box
+  // would leave them.
+  const uint32_t q_stage = kv_addr + kKvStageBytes;
+  static_assert((kStages - 1) * kKvStageBytes >= kHeads * kQStageRow, "the Q staging area must fit behind ring stage 0");
   for (int idx = threadIdx.x; idx < kHeads * kRowChunks; idx += kThreads) {
     const int r = idx / kRowChunks, chunk = idx % kRowChunks;
     const int head = head0 + r;
     const bool valid = head < p.heads;
     const size_t hrow = size_t(b) * p.heads + (valid ? head : 0);
     const __nv_bfloat16* src = chunk < kCkv / 8 ? p.q_nope + hrow * kCkv + chunk * 8 : p.q_pe + hrow * kKpe + (chunk - kCkv / 8) * 8;
-    cp_async_16(q_stage + r * (kRow * 2) + ((chunk ^ (r & 7)) << 4), src, valid);
+    const uint32_t dst = chunk < kQTmemSlabs * 8 ? q_stage + r * kQStageRow + ((chunk ^ (r & 7)) << 4)
+                                                 : q_tail_addr + slab_off(kHeads, r, chunk - kQTmemSlabs * 8);
+    cp_async_16(dst, src, valid);
   }
   cp_async_commit();
   // The first tile goes out while the Q block is in flight (its page lookup is two dependent loads);
@@ -233,8 +247,8 @@ mla_decode_kernel(const Params p) {
       const int s = i % kStages;
       const long long next_slot = i + 1 < tiles ? lookup_row(p, page_base, begin + (i + 1) * kTile, end, threadIdx.x) : -1;
       ok = mbar_wait(&sh->kv_empty[s], ((i / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
-      // stages 2..5 hold the Q block until the softmax warps have moved it to tensor memory
-      if (ok && i == 2) ok = mbar_wait(&sh->q_moved, 0, abort_flag, p.status, kStatusWaitFlag);
+      // stages 1..3 hold the Q block until the softmax warps have moved it to tensor memory
+      if (ok && i == 1) ok = mbar_wait(&sh->q_moved, 0, abort_flag, p.status, kStatusWaitFlag);
       if (!ok) break;
       load_tile(p, my_slot, kv_addr + s * kKvStageBytes, threadIdx.x);
       cp_async_arrive_on(&sh->kv_full[s]);
@@ -259,10 +273,16 @@ mla_decode_kernel(const Params p) {
         // (a slab further every four steps, 32 bytes inside the swizzled row otherwise), so the
         // single issuing thread spends a few instructions per MMA, not a descriptor build.
         const uint64_t b_base = umma_desc_sw128(kv_addr + s * kKvStageBytes);
+        const uint64_t a_base = umma_desc_sw128(q_tail_addr);
 #pragma unroll
         for (int step = 0; step < kRow / 16; ++step) {
           const uint64_t b_desc = b_base + uint64_t(((step >> 2) * kKvSlabBytes + (step & 3) * 32) >> 4);
-          umma_f16_a_tmem(tmem_base + kColS, tmem_base + kColQ + step * 8, b_desc, idesc_qk, step != 0);
+          if (step < kQTmemSlabs * 4) {         // Q dims 0..383 from tensor memory
+            umma_f16_a_tmem(tmem_base + kColS, tmem_base + kColQ + step * 8, b_desc, idesc_qk, step != 0);
+          } else {                              // dims 384..575 from shared memory
+            const uint64_t a_desc = a_base + uint64_t((((step >> 2) - kQTmemSlabs) * kQSlabBytes + (step & 3) * 32) >> 4);
+            umma_f16(tmem_base + kColS, a_desc, b_desc, idesc_qk, 1);
+          }
         }
         tcgen05_commit(&sh->s_full);
       };
@@ -303,16 +323,15 @@ mla_decode_kernel(const Params p) {
     constexpr int kOwnCols = kDimsPerCta / 2;       // O columns per warp group
     bool ok = true;
     {
-      // Q rows, staging area -> tensor memory: 576 bf16 = 288 columns, two elements per column, in the
-      // order of the latent row (512 q_nope, 64 q_pe); group 0 stores columns 0..159, group 1 the
-      // rest.  Heads past the end are rows of zeros.
+      // Q rows, staging area -> tensor memory: dims 0..383 = 192 columns, two elements per column;
+      // group 0 stores columns 0..95, group 1 the rest.  Heads past the end are rows of zeros.
 #pragma unroll 1
-      for (int c = grp * 160; c < (grp == 0 ? 160 : kRow / 2); c += 32) {       // 32 columns = 8 x 16 bytes per store
+      for (int c = grp * (kQTmemCols / 2); c < (grp + 1) * (kQTmemCols / 2); c += 32) {       // 32 columns = 8 x 16 bytes per store
         uint32_t w[32];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const int chunk = c / 4 + k;                // 16-byte chunk of the 1152-byte row
-          const uint4 x = *reinterpret_cast<const uint4*>(base + 2 * kKvStageBytes + r * (kRow * 2) + ((chunk ^ (r & 7)) << 4));
+          const int chunk = c / 4 + k;                // 16-byte chunk of the staged 768 bytes of the row
+          const uint4 x = *reinterpret_cast<const uint4*>(base + kQSmemBytes + kKvStageBytes + r * kQStageRow + ((chunk ^ (r & 7)) << 4));
           w[4 * k] = x.x; w[4 * k + 1] = x.y; w[4 * k + 2] = x.z; w[4 * k + 3] = x.w;
         }
         tmem_st_32x32b_x32(lane_base + kColQ + c, reinterpret_cast<const float*>(w));
@@ -469,7 +488,7 @@ struct Handle {
   Params p;
 };
 
-constexpr int kMaxWorkers = 64;                            // workers the scratch is sized for (SMs / 4 per head block)
+constexpr int kMaxWorkers = 128;                           // workers the scratch is sized for (SMs / 2 per head block)
 
 // Workspace behind the 256-byte status block: tile_prefix [B+1] int | part_o [slots, H, 512] f32 | part_lse [slots, H] f32
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
