@@ -11,16 +11,17 @@
 // of tiles of all sequences, so it works through one to a few sequences in turn); the two halves
 // of a range are neighbouring CTAs, so one of them reads the latent rows from L2.  The 128 heads
 // are the 128 TMEM lanes:
-//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q dims 0..383 from TENSOR memory, 384..575 and
+//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q dims 0..319 from TENSOR memory, 320..575 and
 //                                                        the tile K-major from shared memory
 //   O[128 x 256 dims]  += P[128 x 32] . V[32 x 256]     P from tensor memory, V = the same tile read
 //                                                        MN-major (no transposed copy is made)
-// Tensor memory holds O (256 columns), S (32), P (32) and as much of Q as fits beside them (192
-// columns = 384 of a row's 576 bf16); the rest of Q (48 KiB) stays in shared memory.  All of Q in
+// Tensor memory holds O (256 columns), S (32), two P buffers (32 each, so that the softmax of tile
+// i+1 need not wait for PV(i)) and as much of Q as fits beside them (160 columns = 320 of a row's
+// 576 bf16); the rest of Q (64 KiB) stays in shared memory.  All of Q in
 // shared memory would take 147 KiB, leave room for two ring stages only, and be re-read by every
 // QK (1152 clocks of shared-memory bandwidth per tile); all of Q in tensor memory leaves O only
 // 128 columns, i.e. four CTAs per range that each repeat the QK product AND the softmax.  With the
-// split, 179 KiB of shared memory are a four-stage ring of 32-token tiles (cp.async gather per
+// split, 144 KiB of shared memory are a four-stage ring of 32-token tiles (cp.async gather per
 // token, so any page size works; a stage's barrier is arrived on by the copies themselves).
 // Eight softmax warps, two per head row, read S from TMEM, keep the running max and sum in base
 // 2, and write P back to TMEM as TWO bf16 terms (value + rounding residual; one term is not
@@ -41,8 +42,8 @@ constexpr int kRowChunks = kRow / 8;                       // 72 16-byte chunks 
 constexpr int kHeads = 128;                                // query heads per CTA = TMEM lanes
 constexpr int kDimsPerCta = 256;                           // output dims per CTA (half of ckv)
 constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, tile range)
-constexpr int kQTmemSlabs = 6;                             // Q dims 0..383 live in tensor memory,
-constexpr int kQSmemSlabs = kSlabs - kQTmemSlabs;          //   dims 384..575 (three slabs) in shared memory
+constexpr int kQTmemSlabs = 5;                             // Q dims 0..319 live in tensor memory,
+constexpr int kQSmemSlabs = kSlabs - kQTmemSlabs;          //   dims 320..575 (four slabs) in shared memory
 constexpr int kQTmemCols = kQTmemSlabs * 32;               // 192 columns, two bf16 per column
 constexpr int kQSlabBytes = kHeads * 128;                  // 16 KiB
 constexpr int kQSmemBytes = kQSmemSlabs * kQSlabBytes;     // 48 KiB
@@ -58,8 +59,9 @@ constexpr int kSoftmaxWarps = 8;                           //   (warp - 8) / 4 =
 constexpr int kThreads = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;                   // log2 units
-// tensor-memory columns: O fp32 (256), S fp32 (32), P as two bf16 terms (16 + 16), Q dims 0..383 (192): all 512
-constexpr uint32_t kColO = 0, kColS = kColO + kDimsPerCta, kColP = kColS + kTile, kColQ = kColP + kTile, kTmemColumns = 512;
+// tensor-memory columns: O fp32 (256), S fp32 (32), two P buffers of two bf16 terms each (2 x 32), Q dims 0..319
+// (160): all 512
+constexpr uint32_t kColO = 0, kColS = kColO + kDimsPerCta, kColP = kColS + kTile, kColQ = kColP + 2 * kTile, kTmemColumns = 512;
 static_assert(kColQ + kQTmemCols <= kTmemColumns, "Q does not fit in tensor memory");
 
 struct Params {
@@ -77,7 +79,8 @@ struct Params {
 
 struct Shared {
   uint64_t kv_full[kStages], kv_empty[kStages];
-  uint64_t s_full, s_free, p_ready, pv_done;      // one S and one P buffer: the tensor pipe is in order
+  uint64_t s_full, s_free, p_ready;               // one S buffer: the tensor pipe is in order
+  uint64_t pv_done[2];                            // two P buffers, so that the softmax of tile i+1 need not wait for PV(i)
   uint64_t row_sums;                              // the two softmax warps of a row exchange their sums once
   uint64_t q_moved;                               // Q has left its staging area (ring stages 1..3)
   uint32_t tmem_base;
@@ -199,7 +202,7 @@ mla_decode_kernel(const Params p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->kv_full[s], kLoaderThreads); mbar_init(&sh->kv_empty[s], 1); }
     mbar_init(&sh->s_full, 1); mbar_init(&sh->s_free, kSoftmaxWarps);
-    mbar_init(&sh->p_ready, kSoftmaxWarps); mbar_init(&sh->pv_done, 1);
+    mbar_init(&sh->p_ready, kSoftmaxWarps); mbar_init(&sh->pv_done[0], 1); mbar_init(&sh->pv_done[1], 1);
     mbar_init(&sh->row_sums, kSoftmaxWarps);
     mbar_init(&sh->q_moved, kSoftmaxWarps);
     fence_barrier_init();
@@ -302,11 +305,11 @@ mla_decode_kernel(const Params p) {
         for (int term = 0; term < 2; ++term) {
 #pragma unroll
           for (int ks = 0; ks < kTile / 16; ++ks) {
-            const uint32_t a_tmem = tmem_base + kColP + term * (kTile / 2) + ks * 8;
+            const uint32_t a_tmem = tmem_base + kColP + (i & 1) * kTile + term * (kTile / 2) + ks * 8;
             umma_f16_a_tmem(tmem_base + kColO, a_tmem, v_base + uint64_t((ks * 2048) >> 4), idesc_pv, (i | term | ks) != 0);
           }
         }
-        tcgen05_commit(&sh->pv_done);
+        tcgen05_commit(&sh->pv_done[i & 1]);
         tcgen05_commit(&sh->kv_empty[s]);
       }
     }
@@ -323,10 +326,10 @@ mla_decode_kernel(const Params p) {
     constexpr int kOwnCols = kDimsPerCta / 2;       // O columns per warp group
     bool ok = true;
     {
-      // Q rows, staging area -> tensor memory: dims 0..383 = 192 columns, two elements per column;
+      // Q rows, staging area -> tensor memory: dims 0..319 = 160 columns, two elements per column;
       // group 0 stores columns 0..95, group 1 the rest.  Heads past the end are rows of zeros.
 #pragma unroll 1
-      for (int c = grp * (kQTmemCols / 2); c < (grp + 1) * (kQTmemCols / 2); c += 32) {       // 32 columns = 8 x 16 bytes per store
+      for (int c = grp * 96; c < (grp == 0 ? 96 : kQTmemCols); c += 32) {       // 32 columns = 8 x 16 bytes per store
         uint32_t w[32];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -372,8 +375,8 @@ mla_decode_kernel(const Params p) {
         }
       }
       const float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
-      if (i > 0) {               // P, and O for a rescale, are free once PV(i-1) has completed
-        ok = mbar_wait(&sh->pv_done, (i - 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+      if (i >= 2) {              // this tile's P buffer is free once PV(i-2), which read it, has completed
+        ok = mbar_wait(&sh->pv_done[i & 1], ((i - 2) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
         if (!ok) break;
         tcgen05_fence_after();
       }
@@ -382,6 +385,10 @@ mla_decode_kernel(const Params p) {
       } else {
         const bool need = tmax > m_ref + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {         // both warps of a row see the same logits and decide alike
+          // O is about to be rescaled in tensor memory: PV(i-1) must have landed
+          ok = mbar_wait(&sh->pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+          if (!ok) break;
+          tcgen05_fence_after();
           const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
           if (need) { m_ref = tmax; l *= alpha; }
 #pragma unroll 1
@@ -406,8 +413,8 @@ mla_decode_kernel(const Params p) {
         split_bf16x2(p0, p1, hi[c >> 1], lo[c >> 1]);
       }
       l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
-      tmem_st_32x32b_x8(lane_base + kColP + grp * (kTile / 4), hi);
-      tmem_st_32x32b_x8(lane_base + kColP + kTile / 2 + grp * (kTile / 4), lo);
+      tmem_st_32x32b_x8(lane_base + kColP + (i & 1) * kTile + grp * (kTile / 4), hi);
+      tmem_st_32x32b_x8(lane_base + kColP + (i & 1) * kTile + kTile / 2 + grp * (kTile / 4), lo);
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
@@ -420,7 +427,7 @@ mla_decode_kernel(const Params p) {
       if (lane == 0) mbar_arrive(&sh->row_sums);
       ok = mbar_wait(&sh->row_sums, 0, abort_flag, p.status, kStatusWaitFlag);
     }
-    if (ok) ok = mbar_wait(&sh->pv_done, (tiles - 1) & 1, abort_flag, p.status, kStatusWaitFlag);
+    if (ok) ok = mbar_wait(&sh->pv_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
     if (ok) {
       tcgen05_fence_after();
       const int head = head0 + r;
