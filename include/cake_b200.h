@@ -164,7 +164,8 @@ int cake_b200_moe_intermediate(void* handle, int which, void** device_pointer_ou
  * buffers: q bf16 [B,Hq,D], k_cache bf16 [pages,page_size,Hkv,D], v_cache (same), kv_indptr int32 [B+1] (pages),
  *          kv_indices int32 [*], kv_last_page_len int32 [B] (extension for page_size > 1; the reference has page_size 1),
  *          sm_scale fp32 [1], output bf16 [B,Hq,D], lse fp32 [B,Hq], workspace.  D == 128; Hq/Hkv in 1..8;
- *          batch <= 65535; max_kv_len <= 2^21.  A launch is two kernels (work list, then decode + merge).
+ *          batch <= 65535; max_kv_len <= 2^21.  A launch is two kernels (work list, then decode + merge); the
+ *          work is cut on the device from the sequence lengths, so max_kv_len does not enter the workspace size.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   int64_t batch;
@@ -185,9 +186,8 @@ int cake_b200_gqa_decode_destroy(void* handle);
  * allocation can imply.  The work list, the counters and the split-KV partial results go to a fixed 16 MiB array inside the library image
  * (cake_b200_gqa_decode_noalloc_scratch_limit() returns the size); every GPU that loads the library holds that
  * array until the process exits.  The call uses no cudaMalloc / cudaFree and no allocating library routine.
- *   - Limit: batch * (max_kv_len / chunk + 1) * (num_qo_heads * 129 * 4 + 16) bytes must fit in the array; the call
- *     lengthens its KV chunks (up to 1024 tokens) to make it fit and returns CAKE_B200_ERR_WORKSPACE (20004) when
- *     it still cannot.
+ *   - Limit: (token ranges + batch) * (num_qo_heads * 129 * 4 + 24) bytes must fit in the array, token ranges being
+ *     the SM count (times 8 / num_kv_heads below 8 KV heads); otherwise CAKE_B200_ERR_WORKSPACE (20004).
  *   - The first call on each device looks up the array's device address and sets the kernel's shared-memory
  *     attribute (with that device current); make that first call before starting any stream capture.
  *   - All calls share the array.  Nothing in it has to be cleared: every call rewrites its queue, counters and

@@ -5,21 +5,21 @@
 // lse = logsumexp / ln 2; an empty sequence gives zeros and -inf.
 //
 // The kernel is bound by the HBM stream of K and V (2 * Hkv * D * 2 bytes per token) and never
-// writes logits or probabilities to memory.  Work is cut into items (sequence, KV chunk, KV
-// head) that a one-CTA plan kernel lists on the device; the decode kernel is persistent, one CTA of
-// sixteen warps per SM, and each PAIR of warps (w, w+8) pulls items from an atomic queue on its
-// own, so the pairs of an SM drift apart and one pair's start-up and wind-down are covered by the
-// seven others' streaming.  The two warps of a pair take alternate 16-token tiles of the item and run
-// their own cp.async rings (128-bit copies, one 256-byte row per token and head, XOR-swizzled in
-// shared memory, K and V halves of a tile in separate slots); there is no CTA-wide barrier.
-// Neighbouring pairs start on neighbouring KV heads of the same tokens, which keeps the DRAM
-// accesses inside whole pages (page_size * Hkv * 256 B contiguous).  The G = Hq/Hkv query heads
-// that share a KV head are the rows of an m16n8k16 bf16 MMA for S = Q K^T (ldmatrix on the K tile;
-// rows beyond G are zero) and the columns of O^T += V^T P^T (ldmatrix.trans on the V tile; P as
-// two bf16 terms, so the weights keep ~16 significant bits); the online softmax runs in base 2
-// with warp shuffles.  The pair merges through shared memory and writes one partial result per
-// item; the pair that finishes the last item of a (sequence, KV head) merges its chunks and writes the
-// output, so there is no separate reduce launch.
+// writes logits or probabilities to memory.  The tokens of all sequences, in order, form one list,
+// and it is cut into as many equal consecutive ranges as there are SMs (a one-CTA plan kernel
+// lists the pieces of sequences each range holds).  The decode kernel is persistent, one CTA of
+// sixteen warps per SM: the CTA takes one range and each PAIR of warps (w, w+8) one KV head of it,
+// so the eight pairs stream whole pages (page_size * Hkv * 256 B contiguous) and every SM moves
+// the same number of bytes whatever the sequence lengths are.  The two warps of a pair take
+// alternate 16-token tiles and run their own cp.async rings (128-bit copies, one 256-byte row per
+// token and head, XOR-swizzled in shared memory, K and V halves of a tile in separate slots);
+// there is no CTA-wide barrier, and a ring does not drain where a range passes from one sequence
+// to the next.  The G = Hq/Hkv query heads that share a KV head are the rows of an m16n8k16 bf16
+// MMA for S = Q K^T (ldmatrix on the K tile; rows beyond G are zero) and the columns of
+// O^T += V^T P^T (ldmatrix.trans on the V tile; P as two bf16 terms, so the weights keep ~16
+// significant bits); the online softmax runs in base 2 with warp shuffles.  The pair merges through
+// shared memory and writes one partial result per piece; the pair that finishes the last piece of
+// a (sequence, KV head) merges the pieces and writes the output, so there is no reduce launch.
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <mutex>
@@ -38,10 +38,8 @@ constexpr int kTileBytes = kTile * kD * 2;          // 4 KiB: 16 tokens of K (or
 constexpr int kWarpSmem = kSlots * kTileBytes;       // 12 KiB
 constexpr int kRingBytes = kWarps * kWarpSmem;       // 192 KiB per CTA, one CTA per SM
 constexpr int kParkBytes = 34 * 32 * 4;               // a warp's O^T (32 registers), m and l
-constexpr int kSmemBytes = kRingBytes + kHeads * (kParkBytes + 32);   // + per pair: parked state, 32-byte mailbox
+constexpr int kSmemBytes = kRingBytes + kHeads * kParkBytes;          // + per pair: the second warp's parked state
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kGuideDiv = 2;            // guided chunk: half of what is left per worker ...
-constexpr int kGuideMin = 192;          // ... but at least 192 tokens: below that the per-item costs outweigh the balance
 
 struct Params {
   const __nv_bfloat16* q;        // [B, Hq, D]
@@ -55,11 +53,14 @@ struct Params {
   float* lse;                    // [B, Hq]
   float* part_o;                 // [capacity, Hq, D] normalised partial outputs, one slot per entry of `items`
   float* part_lse;               // [capacity, Hq]    base-2 partial log-sum-exp
-  int4* items;                   // [capacity] chunks of sequences, written by the plan kernel (see item_* below)
+  int4* items;                   // [capacity] pieces of sequences in token order, written by the plan kernel:
+                                 //   x = b | (pieces of b << 16), y = first token, z = list index of b's first piece, w = end token
+  int* item_page;                // [capacity] kv_indptr[b] of the piece
+  int* range_first;              // [ranges + 1] list index of the first piece of each token range
   int* ctrl;                     // [0] work queue cursor, [1] number of entries of `items`
   int* done;                     // [B, Hkv] finished items
   int* status;                   // library status word (may be null)
-  int batch, hq, hkv, page_size, chunk, capacity, workers;
+  int batch, hq, hkv, page_size, capacity, ranges;
 };
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
@@ -123,62 +124,44 @@ __device__ __forceinline__ void load_half(const __nv_bfloat16* __restrict__ cach
   }
 }
 
-// An entry of the work list is one chunk of one sequence:
-//   x = b | (chunks of b << 16),  y = (begin / 64) << 11 | tokens,  z = list index of b's first chunk,  w = kv_indptr[b].
-// Entry i owns partial-result slot i; with Hkv KV heads it stands for Hkv items of the queue.
-__device__ __forceinline__ int item_begin(const int4& r) { return (r.y >> 11) * 64; }
-__device__ __forceinline__ int item_tokens(const int4& r) { return r.y & 2047; }
-
-// Chunk size for a sequence that starts when `remaining` tokens (over all sequences, in list
-// order) are still to be listed.  Guided sizes: a fixed share of what is left per worker, between
-// kGuideMin tokens and the base chunk, in multiples of 64 -- full-size chunks first, smaller ones
-// towards the end of the queue, so that the workers run dry at nearly the same time.
-__device__ __forceinline__ int chunk_at(const Params& p, long long remaining, bool guided, float share) {
-  if (!guided) return p.chunk;
-  const int c = int(fminf(float(remaining) * share, 4096.f)) & ~63;
-  return c < kGuideMin ? min(kGuideMin, p.chunk) : min(c, p.chunk);
-}
-
-// One CTA: lists the chunks of this launch, resets the queue and the counters, and writes the
-// results of empty sequences (zeros, lse = -inf), which no item covers.  All chunks of a sequence
-// have one size.  The kernel sits on the critical path of every decode step, so a batch of up to
-// 1024 sequences is planned in one sweep: one load round trip, two scans, the list.
+// One CTA: cuts the list of all tokens into p.ranges equal ranges (a multiple of the 16-token
+// tile each) and lists the pieces of sequences they hold, in token order, so that the pieces of a
+// range, and the pieces of a sequence, are consecutive entries.  Also resets the counters and writes
+// the results of empty sequences (zeros, lse = -inf), which no piece covers.
 __global__ void __launch_bounds__(1024)
 gqa_plan_kernel(const Params p) {
   __shared__ long long sums64[32];
   __shared__ int sums32[32];
   const int tid = threadIdx.x;
-#if __CUDA_ARCH__ >= 900
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the decode grid may take its SMs and wait
-#endif
   if (tid == 0 && p.status) *p.status = 0;
-  const float share = float(p.hkv) / (float(p.workers) * float(kGuideDiv));   // of the remaining tokens: one chunk
-
   const int len0 = tid < p.batch ? seq_len(p, tid) : 0;              // the first 1024 lengths stay in registers
   long long mine = len0, all_tokens = 0;
   for (int b = tid + 1024; b < p.batch; b += 1024) mine += seq_len(p, b);
   cta1024_exclusive_scan(mine, sums64, all_tokens);
+  const long long per = max(16LL, (((all_tokens + p.ranges - 1) / p.ranges) + 15) & ~15LL);
 
-  bool guided = true;
-  for (int pass = 0; pass < 2; ++pass) {       // a second time only if the guided list does not fit
+  int entries = 0;
+  for (int pass = 0; pass < 2; ++pass) {        // count, then write
     long long tokens_before = 0;
     int entries_before = 0;
     for (int base = 0; base < p.batch; base += 1024) {
       const int b = base + tid;
       const int len = base == 0 ? len0 : (b < p.batch ? seq_len(p, b) : 0);
-      long long batch_tokens = len;
-      long long start = tokens_before;
-      if (p.batch > 1024 || guided) start += cta1024_exclusive_scan((long long)len, sums64, batch_tokens);
-      const int c = chunk_at(p, all_tokens - start, guided, share);
-      const int n = (len + c - 1) / c;
+      long long batch_tokens;
+      const long long start = tokens_before + cta1024_exclusive_scan((long long)len, sums64, batch_tokens);
+      const int first_range = int(start / per);
+      const int n = len > 0 ? int((start + len - 1) / per) - first_range + 1 : 0;
       int batch_entries;
       const int first = entries_before + cta1024_exclusive_scan(n, sums32, batch_entries);
-      const bool fits = !guided || entries_before + batch_entries <= p.capacity;     // uniform for the CTA
-      if (fits && b < p.batch) {
-        // Entries written while a later batch turns out not to fit are simply written again.
+      if (pass == 1 && b < p.batch) {
         const int page_base = p.kv_indptr[b];
-        for (int k = 0; k < n; ++k)
-          p.items[first + k] = make_int4(b | (n << 16), ((k * c / 64) << 11) | min(c, len - k * c), first, page_base);
+        for (int k = 0; k < n; ++k) {
+          const long long range_start = (long long)(first_range + k) * per;
+          const long long piece_begin = max(start, range_start), piece_end = min(start + len, range_start + per);
+          p.items[first + k] = make_int4(b | (n << 16), int(piece_begin - start), first, int(piece_end - start));
+          p.item_page[first + k] = page_base;
+          if (piece_begin == range_start) p.range_first[first_range + k] = first + k;
+        }
         for (int h = 0; h < p.hkv; ++h) p.done[size_t(b) * p.hkv + h] = 0;
         if (len == 0) {
           for (int h = 0; h < p.hq; ++h) {
@@ -189,16 +172,12 @@ gqa_plan_kernel(const Params p) {
       }
       tokens_before += batch_tokens;
       entries_before += batch_entries;
-      if (!fits) break;
     }
-    if (!guided || entries_before <= p.capacity) {
-      if (tid == 0) {
-        p.ctrl[0] = p.workers;        // the first item of each worker follows from its index
-        p.ctrl[1] = entries_before;
-      }
-      break;
+    if (pass == 0) {
+      entries = entries_before;
+      for (int r = tid; r <= p.ranges; r += 1024) p.range_first[r] = entries;     // ranges past the last token hold nothing
+      __syncthreads();
     }
-    guided = false;
   }
 }
 
@@ -280,25 +259,43 @@ gqa_decode_kernel(const Params p) {
   const float scale2 = __ldg(p.sm_scale) * kLog2e;
   const uint32_t ring = smem_u32(smem) + warp * kWarpSmem;
   float* park = reinterpret_cast<float*>(smem + kRingBytes + pair * kParkBytes);
-  volatile int* mailbox = reinterpret_cast<volatile int*>(smem + kRingBytes + kHeads * kParkBytes + pair * 32);
 
   const uint64_t stream_policy = l2_policy_evict_first(), keep_policy = l2_policy_evict_last();
+  // Which token range and which KV head this pair works on.  With eight or more KV heads a CTA
+  // takes one range and eight heads of it; with 1, 2 or 4 the CTA's pairs share 8 / Hkv ranges.
+  int range_id, kvh_mine;
+  bool active;
+  if (p.hkv >= kHeads) {
+    const int head_blocks = (p.hkv + kHeads - 1) / kHeads;
+    range_id = blockIdx.x / head_blocks;
+    kvh_mine = (blockIdx.x % head_blocks) * kHeads + pair;
+    active = kvh_mine < p.hkv && range_id < p.ranges;
+  } else if (kHeads % p.hkv == 0) {
+    range_id = blockIdx.x * (kHeads / p.hkv) + pair / p.hkv;
+    kvh_mine = pair % p.hkv;
+    active = range_id < p.ranges;
+  } else {
+    range_id = blockIdx.x;
+    kvh_mine = pair;
+    active = pair < p.hkv && range_id < p.ranges;
+  }
   // Launched as a programmatic dependent of the plan kernel: everything above overlaps it, the
   // list and the counters are read only after it has completed.
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int total = p.ctrl[1] * p.hkv;  // items: entries of the list x KV heads, KV head fastest
-  // A pair's first item is fixed by its index; every later one is drawn from the queue while the
-  // item before it runs, by the first lane of the pair's first warp, which hands the answer to
-  // the second warp through the pair's mailbox in shared memory (words 0-4, then the item's
-  // serial number in word 5).
-  int idx = blockIdx.x * kHeads + pair;
+  // Items are numbered piece * Hkv + KV head; this pair's run from idx up to (not including) total.
+  int idx = 0, total = 0;
+  if (active) {
+    idx = p.range_first[range_id] * p.hkv + kvh_mine;
+    total = p.range_first[range_id + 1] * p.hkv;
+  }
   int4 rec = make_int4(0, 0, 0, 0);
-  if (idx < total) rec = __ldg(p.items + idx / p.hkv);
-  if (part == 0 && lane == 0) mailbox[5] = -1;
-  __syncthreads();                      // the only CTA-wide barrier: every warp is still here
-  int serial = 0;
+  int page_base = 0;
+  if (idx < total) {
+    rec = __ldg(p.items + idx / p.hkv);
+    page_base = __ldg(p.item_page + idx / p.hkv);
+  }
   auto tiles_of = [&](int item, const int4& r) {    // tiles of an item that fall to this warp
-    return item < total ? ((item_tokens(r) + kTile - 1) / kTile - part + kParts - 1) / kParts : 0;
+    return item < total ? ((r.w - r.y + kTile - 1) / kTile - part + kParts - 1) / kParts : 0;
   };
   // Q fragments (A operand of S = Q K^T): rows = heads of the group, zero beyond it.
   uint32_t qa[8][2];
@@ -324,17 +321,17 @@ gqa_decode_kernel(const Params p) {
   while (idx < total) {
     const int kvh = idx % p.hkv;
     const int b = rec.x & 0xffff, chunks = int(unsigned(rec.x) >> 16);
-    const int begin = item_begin(rec), end = begin + item_tokens(rec), page_base = rec.w;
+    const int begin = rec.y, end = rec.w;
     const int my_tiles = tiles_of(idx, rec);
-    // Next item: drawn now, its record fetched one tile later and published one tile after that,
-    // so that neither memory round trip stalls the stream; both warps need it at their last tile,
-    // where the first copies of the next item go out.
-    int drawn_idx = total;
-    int4 drawn_rec = make_int4(0, 0, 0, 0);
-    if (part == 0 && lane == 0) drawn_idx = atomicAdd(p.ctrl, 1);
-    int nxt_idx = total;
+    // The next piece of the range (same KV head): its record is asked for now and needed at this
+    // item's last tile, where the first copies of the next item go out.
+    const int nxt_idx = idx + p.hkv;
     int4 nxt_rec = make_int4(0, 0, 0, 0);
-    bool know_next = false;
+    int nxt_page = 0;
+    if (nxt_idx < total) {
+      nxt_rec = __ldg(p.items + nxt_idx / p.hkv);
+      nxt_page = __ldg(p.item_page + nxt_idx / p.hkv);
+    }
     if (my_tiles > 0 && !primed) {      // cold start: nothing of this item is in flight yet
       const int v_slot = k_slot == 2 ? 0 : k_slot + 1;
       next_row = lookup_rows(p, page_base, kvh, begin + part * kTile, end, lane);
@@ -359,39 +356,12 @@ gqa_decode_kernel(const Params p) {
       const int tok0 = begin + (part + j * kParts) * kTile;
       // the tile after this one in the stream: the item's next, or the first of the coming item
       const bool last = j + 1 == my_tiles;
-      if (part == 0) {
-        if (j == min(1, my_tiles - 1) && lane == 0 && drawn_idx < total) drawn_rec = __ldg(p.items + drawn_idx / p.hkv);
-        if (j == min(2, my_tiles - 1) && lane == 0) {
-          mailbox[0] = drawn_rec.x; mailbox[1] = drawn_rec.y; mailbox[2] = drawn_rec.z; mailbox[3] = drawn_rec.w;
-          mailbox[4] = drawn_idx;
-          __threadfence_block();
-          mailbox[5] = serial;
-        }
-      }
-      if (last) {
-        if (part == 0) {
-          nxt_idx = __shfl_sync(0xffffffffu, drawn_idx, 0);
-          nxt_rec = make_int4(__shfl_sync(0xffffffffu, drawn_rec.x, 0), __shfl_sync(0xffffffffu, drawn_rec.y, 0),
-                              __shfl_sync(0xffffffffu, drawn_rec.z, 0), __shfl_sync(0xffffffffu, drawn_rec.w, 0));
-          know_next = true;
-        } else {
-          // Normally published long ago.  If not, go on without the early copies: the record is
-          // read again behind the pair's barrier below.
-          for (int spin = 0; spin < 4096 && !know_next; ++spin) know_next = mailbox[5] == serial;
-          if (know_next) {
-            __threadfence_block();
-            nxt_rec = make_int4(mailbox[0], mailbox[1], mailbox[2], mailbox[3]);
-            nxt_idx = mailbox[4];
-          }
-        }
-      }
-      const int nxt_tiles = know_next ? tiles_of(nxt_idx, nxt_rec) : 0;
+      const int nxt_tiles = tiles_of(nxt_idx, nxt_rec);
       const bool follows = !last || nxt_tiles > 0;
       cp_async_wait<1>();
       __syncwarp();                     // K(t) has landed; every lane is done with V(t-1)
       if (follows) {
-        next_row = last ? lookup_rows(p, nxt_rec.w, nxt_idx % p.hkv, item_begin(nxt_rec) + part * kTile,
-                                      item_begin(nxt_rec) + item_tokens(nxt_rec), lane)
+        next_row = last ? lookup_rows(p, nxt_page, kvh, nxt_rec.y + part * kTile, nxt_rec.w, lane)
                         : lookup_rows(p, page_base, kvh, tok0 + kParts * kTile, end, lane);
         load_half(p.k_cache, next_row, ring + free_slot * kTileBytes, lane, stream_policy);
       }
@@ -459,7 +429,7 @@ gqa_decode_kernel(const Params p) {
       k_slot = free_slot;
       primed = last && follows;
     }
-    if (know_next) load_q(nxt_idx, nxt_rec);   // the Q registers are free: fetch the coming item's
+    load_q(nxt_idx, nxt_rec);           // the Q registers are free: fetch the coming item's
 
     if (part == 1) {                    // the second warp parks its state for the first
 #pragma unroll
@@ -469,12 +439,7 @@ gqa_decode_kernel(const Params p) {
       park[32 * 32 + lane] = m;
       park[33 * 32 + lane] = l;
     }
-    pair_barrier(pair);                 // parked state and mailbox are written
-    if (!know_next) {                   // a warp without tiles in this item, or one that gave up waiting
-      nxt_rec = make_int4(mailbox[0], mailbox[1], mailbox[2], mailbox[3]);
-      nxt_idx = mailbox[4];
-      load_q(nxt_idx, nxt_rec);
-    }
+    pair_barrier(pair);                 // the parked state is written
     float f00 = 0.f, f01 = 0.f, f10 = 0.f, f11 = 0.f;
     if (part == 0) {                    // fold the partner's state into the registers
       const float m1 = park[32 * 32 + lane], l1 = park[33 * 32 + lane];
@@ -493,7 +458,7 @@ gqa_decode_kernel(const Params p) {
         o[n][3] = o[n][3] * f01 + park[(n * 4 + 3) * 32 + lane] * f11;
       }
     }
-    pair_barrier(pair);                 // parked state and mailbox have been read
+    pair_barrier(pair);                 // the parked state has been read
     if (part == 0) {
       // partial result of this item: normalised rows and base-2 log-sum-exp
       const size_t slot0 = size_t(idx / p.hkv) * p.hq + kvh * group;
@@ -520,52 +485,57 @@ gqa_decode_kernel(const Params p) {
         merge_chunks(p, b, kvh, rec.z, chunks, group, lane);
       }
     }
-    idx = nxt_idx; rec = nxt_rec;
-    ++serial;
+    idx = nxt_idx; rec = nxt_rec; page_base = nxt_page;
   }
   cp_async_wait<0>();
 }
 
 struct Handle {
   int device;
+  int sms;
   Params p;
 };
 
-inline int pick_chunk(const cake_b200_gqa_decode_config& c, int sms) {
-  // Base chunk: the size of the items at the head of the queue (the plan kernel shrinks them
-  // towards its end).  Long enough that the per-item costs (merge of the two warps, partial
-  // result, counter) vanish, short enough that even base-size chunks alone would give every warp
-  // pair a few items on sequences of half the maximum length.  A multiple of 64 tokens.
-  int chunk = 512;
-  const long long max_len = c.max_kv_len > 0 ? c.max_kv_len : 1;
-  while (chunk > 64 && (long long)c.batch * c.num_kv_heads * ((max_len / 2 + chunk - 1) / chunk) < 2LL * kHeads * sms) chunk >>= 1;
-  return chunk;
+// Token ranges and CTAs for `sms` SMs: with eight or more KV heads a CTA takes one range and a block
+// of eight heads; with 1, 2 or 4 its eight warp pairs share 8 / Hkv ranges; otherwise a CTA takes
+// one range and leaves the pairs beyond Hkv idle.
+inline void geometry(int hkv, int sms, int* ranges, int* grid) {
+  if (hkv >= kHeads) {
+    const int head_blocks = (hkv + kHeads - 1) / kHeads;
+    *ranges = sms / head_blocks > 0 ? sms / head_blocks : 1;
+    *grid = *ranges * head_blocks;
+  } else {
+    *ranges = kHeads % hkv == 0 ? sms * (kHeads / hkv) : sms;
+    *grid = sms;
+  }
 }
+constexpr int kMaxSms = 192;             // SM count the workspace is sized for
 
-// Entries of the work list that always suffice with base-size chunks, and the room that lets the
-// plan kernel use guided sizes (about 16 smaller chunks per worker near the end of the queue).
-inline size_t uniform_entries(const cake_b200_gqa_decode_config& c, int chunk) {
-  return size_t(c.batch) * (size_t((c.max_kv_len + chunk - 1) / chunk) + 1);
-}
-inline size_t guided_entries(const cake_b200_gqa_decode_config& c, int chunk) {
-  return uniform_entries(c, chunk) + size_t(16 * kHeads * 148) / c.num_kv_heads + 64;
+// A range holds a piece of every sequence it touches: at most ranges + batch pieces in all.
+inline size_t entries_for(const cake_b200_gqa_decode_config& c, int sms) {
+  int ranges, grid;
+  geometry(c.num_kv_heads, sms, &ranges, &grid);
+  return size_t(ranges) + size_t(c.batch);
 }
 
 // Scratch layout shared by the two entry points (offsets from a 256-byte aligned base):
-//   [0, 256)  ctrl   | done [B*Hkv] int | items [entries] int4 | part_o [entries*Hq*D] f32 | part_lse [entries*Hq] f32
+//   done [B*Hkv] int | items [entries] int4 | item_page [entries] int | range_first [ranges+1] int |
+//   part_o [entries*Hq*D] f32 | part_lse [entries*Hq] f32
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 inline size_t scratch_bytes(const cake_b200_gqa_decode_config& c, size_t entries) {
-  return 256 + align256(size_t(c.batch) * c.num_kv_heads * sizeof(int)) + align256(entries * sizeof(int4)) +
+  return align256(size_t(c.batch) * c.num_kv_heads * sizeof(int)) + align256(entries * sizeof(int4)) + 2 * align256((entries + 1) * sizeof(int)) +
          align256(entries * c.num_qo_heads * kD * sizeof(float)) + align256(entries * c.num_qo_heads * sizeof(float));
 }
 inline void carve_scratch(Params& p, uint8_t* base) {
   const size_t entries = size_t(p.capacity);
-  p.ctrl = reinterpret_cast<int*>(base);
-  base += 256;
   p.done = reinterpret_cast<int*>(base);
   base += align256(size_t(p.batch) * p.hkv * sizeof(int));
   p.items = reinterpret_cast<int4*>(base);
   base += align256(entries * sizeof(int4));
+  p.item_page = reinterpret_cast<int*>(base);
+  base += align256((entries + 1) * sizeof(int));
+  p.range_first = reinterpret_cast<int*>(base);          // ranges + 1 <= entries + 1
+  base += align256((entries + 1) * sizeof(int));
   p.part_o = reinterpret_cast<float*>(base);
   base += align256(entries * p.hq * kD * sizeof(float));
   p.part_lse = reinterpret_cast<float*>(base);
@@ -593,16 +563,9 @@ inline int fill_params(Params& p, void** buffers, const cake_b200_gqa_decode_con
   return 0;
 }
 
-// One persistent CTA per SM, but never more workers than there can be items.
-inline int grid_for(const Params& p, int sms) {
-  const long long items = (long long)p.capacity * p.hkv;
-  const long long ctas = (items + kHeads - 1) / kHeads;
-  return int(ctas < sms ? (ctas < 1 ? 1 : ctas) : sms);
-}
-
 inline int launch(Params& p, int sms, cudaStream_t s) {
-  const int grid = grid_for(p, sms);
-  p.workers = grid * kHeads;
+  int grid;
+  geometry(p.hkv, sms, &p.ranges, &grid);
   gqa_plan_kernel<<<1, 1024, 0, s>>>(p);
   // The decode grid is a programmatic dependent: it may start while the plan kernel runs and waits
   // for it on the device, which takes the second launch latency off the critical path.
@@ -625,7 +588,7 @@ inline int launch(Params& p, int sms, cudaStream_t s) {
 
 static bool gqa_config_ok(const cake_b200_gqa_decode_config& c) {
   if (c.batch < 0 || c.batch > 65535 || c.head_dim != cake::gqa::kD || c.page_size <= 0 || c.max_kv_len < 0) return false;
-  if (c.max_kv_len > (1 << 21)) return false;             // at most 2^15 chunks of 64 tokens per sequence
+  if (c.max_kv_len > (1 << 21) || c.batch * c.max_kv_len >= (1LL << 40)) return false;
   if (c.num_kv_heads <= 0 || c.num_kv_heads > 65535 || c.num_qo_heads % c.num_kv_heads) return false;
   const int g = c.num_qo_heads / c.num_kv_heads;
   return g >= 1 && g <= 8;
@@ -638,7 +601,7 @@ static int gqa_sm_count(int device, int* sms) {
 
 extern "C" size_t cake_b200_gqa_decode_workspace_bytes(const cake_b200_gqa_decode_config* c) {
   if (!c || !gqa_config_ok(*c)) return 0;
-  return 256 + cake::gqa::scratch_bytes(*c, cake::gqa::guided_entries(*c, cake::gqa::pick_chunk(*c, 148))) + 256;
+  return 256 + cake::gqa::scratch_bytes(*c, cake::gqa::entries_for(*c, cake::gqa::kMaxSms)) + 256;
 }
 
 extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_decode_config* config, void** handle_out) {
@@ -653,8 +616,7 @@ extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_d
   h->device = device;
   gqa::Params& p = h->p;
   if (int rc = gqa::fill_params(p, buffers, *config)) { delete h; return rc; }
-  p.chunk = gqa::pick_chunk(*config, 148);
-  p.capacity = int(gqa::guided_entries(*config, p.chunk));
+  p.capacity = int(gqa::entries_for(*config, gqa::kMaxSms));
   p.status = static_cast<int*>(buffers[9]);               // first word of the workspace
   uint8_t* ws = static_cast<uint8_t*>(buffers[9]) + 256;
   ws += (256 - (reinterpret_cast<uintptr_t>(ws) & 255)) & 255;
@@ -663,7 +625,7 @@ extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_d
   int rc = gqa_sm_count(device, &sms);
   if (!rc) rc = int(cudaFuncSetAttribute(gqa::gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gqa::kSmemBytes));
   if (rc) { delete h; return rc; }
-  p.workers = sms;                                        // the SM count until launch turns it into workers
+  h->sms = sms < gqa::kMaxSms ? sms : gqa::kMaxSms;
   *handle_out = h;
   return 0;
 }
@@ -677,7 +639,7 @@ extern "C" int cake_b200_gqa_decode_launch(void* handle, void* cuda_stream) {
   if (device != h->device) return kErrWrongDevice;
   if (h->p.batch == 0) return 0;
   gqa::Params p = h->p;
-  return gqa::launch(p, h->p.workers, reinterpret_cast<cudaStream_t>(cuda_stream));
+  return gqa::launch(p, h->sms, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
 
 extern "C" int cake_b200_gqa_decode_destroy(void* handle) {
@@ -747,21 +709,15 @@ extern "C" int cake_b200_gqa_decode_noalloc(void** buffers, const cake_b200_gqa_
   gqa::Params p;
   if (int rc = gqa::fill_params(p, buffers, *config)) return rc;
   if (p.batch == 0) return 0;
-  // Same chunking as the workspace variant; longer chunks (fewer partial results) if that is what
-  // it takes to fit the fixed scratch, and a refusal if even two chunks per sequence do not fit.
-  p.chunk = gqa::pick_chunk(*config, 148);
-  while (gqa::scratch_bytes(*config, gqa::uniform_entries(*config, p.chunk)) > gqa::kNoAllocScratchBytes && p.chunk < config->max_kv_len &&
-         p.chunk < 1024)
-    p.chunk *= 2;
-  size_t entries = gqa::uniform_entries(*config, p.chunk);
+  int sms = 0;
+  if (int rc = gqa_sm_count(device, &sms)) return rc;
+  if (sms > gqa::kMaxSms) sms = gqa::kMaxSms;
+  // The work list, the counters and one partial result per (token range, sequence) piece must fit.
+  const size_t entries = gqa::entries_for(*config, sms);
   if (gqa::scratch_bytes(*config, entries) > gqa::kNoAllocScratchBytes) return kErrWorkspace;   // batch * heads too large for 16 MiB
-  // whatever room is left lets the plan kernel use guided chunk sizes
-  while (entries < gqa::guided_entries(*config, p.chunk) && gqa::scratch_bytes(*config, entries + 64) <= gqa::kNoAllocScratchBytes) entries += 64;
   p.capacity = int(entries);
   void* scratch = nullptr;
   if (int rc = gqa::noalloc_setup(device, &scratch)) return rc;
   gqa::carve_scratch(p, static_cast<uint8_t*>(scratch));
-  int sms = 0;
-  if (int rc = gqa_sm_count(device, &sms)) return rc;
   return gqa::launch(p, sms, reinterpret_cast<cudaStream_t>(cuda_stream));
 }

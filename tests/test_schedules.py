@@ -4,8 +4,9 @@ the properties the kernels rely on (no GPU needed).
 * MLA (csrc/decode_mla.cu, mla_plan_kernel / tiles_per_worker): the 32-token tiles of all sequences form
   one list; worker w of W takes the w-th of W equal consecutive ranges; a (worker, sequence) pair
   that meets writes its partial result to slot worker + sequence.
-* GQA (csrc/decode_gqa.cu, gqa_plan_kernel / chunk_at): every sequence is cut into chunks of one
-  size, a multiple of 64 tokens between 192 and the base chunk, chosen from the work left.
+* GQA (csrc/decode_gqa.cu, gqa_plan_kernel): the tokens of all sequences form one list, cut into equal
+  consecutive ranges (a multiple of the 16-token tile); the pieces of sequences the ranges hold are
+  listed in token order, so the pieces of a range, and the pieces of a sequence, are consecutive.
 """
 import random
 
@@ -68,34 +69,55 @@ def test_mla_ranges_cover_every_tile_once_and_slots_are_unique(seed):
     assert max(load.values(), default=0) <= per
 
 
-def gqa_chunks(lens, hkv, workers, base, guide_div=2, guide_min=192):
+def gqa_pieces(lens, ranges):
     total = sum(lens)
-    share = float(hkv) / (float(workers) * guide_div)
-    out, before = [], 0
+    per = max(16, (((total + ranges - 1) // ranges) + 15) & ~15)
+    items, range_first, start = [], None, 0
+    counts = []
     for n in lens:
-        c = int(min((total - before) * share, 4096.0)) & ~63
-        c = min(guide_min, base) if c < guide_min else min(c, base)
-        out.append([(pos, min(c, n - pos)) for pos in range(0, n, c)])
-        before += n
-    return out
+        first_range = start // per
+        counts.append((start + n - 1) // per - first_range + 1 if n > 0 else 0)
+        start += n
+    range_first = [sum(counts)] * (ranges + 1)
+    start = 0
+    for b, n in enumerate(lens):
+        first = len(items)
+        for k in range(counts[b]):
+            range_start = (start // per + k) * per
+            begin, end = max(start, range_start), min(start + n, range_start + per)
+            if begin == range_start:
+                range_first[start // per + k] = len(items)
+            items.append((b, counts[b], begin - start, first, end - start))
+        start += n
+    return items, range_first, per
 
 
-@pytest.mark.parametrize("seed", range(4))
-def test_gqa_chunks_tile_every_sequence(seed):
+@pytest.mark.parametrize("seed", range(5))
+def test_gqa_ranges_partition_the_token_list(seed):
     rng = random.Random(100 + seed)
-    lens = [rng.choice([0, 1, 63, 64, 65, 700, 4096, rng.randrange(0, 5000)]) for _ in range(rng.choice([1, 5, 64]))]
-    base = rng.choice([64, 256, 512])
-    chunks = gqa_chunks(lens, hkv=8, workers=1184, base=base)
-    sizes = set()
-    for n, seq in zip(lens, chunks):
+    lens = [rng.choice([0, 1, 15, 16, 17, 700, 4096, rng.randrange(0, 5000)]) for _ in range(rng.choice([1, 5, 64]))]
+    ranges = rng.choice([1, 18, 148, 1184])
+    items, range_first, per = gqa_pieces(lens, ranges)
+    assert per % 16 == 0 and len(items) <= ranges + len(lens)
+    # pieces of a sequence: consecutive entries, tiling it exactly
+    for b, n in enumerate(lens):
+        mine = [(i, it) for i, it in enumerate(items) if it[0] == b]
+        assert [i for i, _ in mine] == list(range(mine[0][0], mine[0][0] + len(mine))) if mine else n == 0
         pos = 0
-        for begin, tokens in seq:
-            assert begin == pos and begin % 64 == 0 and 0 < tokens <= 1024     # what the record packs: begin/64, 11 bits of tokens
-            pos += tokens
+        for i, (_, count, begin, first, end) in mine:
+            assert count == len(mine) and first == mine[0][0] and begin == pos and end > begin
+            pos = end
         assert pos == n
-        if len(seq) > 1:
-            sizes.add(seq[0][1])
-    assert all(s % 64 == 0 and min(192, base) <= s <= base for s in sizes)
-    # sizes never grow along the list: the head of the queue has the largest chunks
-    firsts = [seq[0][1] for seq in chunks if len(seq) > 1]
-    assert firsts == sorted(firsts, reverse=True)
+    # pieces of a range: entries range_first[r] .. range_first[r+1], all inside the range, `per` tokens unless it is the last
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    assert range_first[0] == 0 or sum(lens) == 0
+    for r in range(ranges):
+        lo, hi = range_first[r], range_first[r + 1]
+        assert lo <= hi
+        tokens = 0
+        for b, _, begin, _, end in items[lo:hi]:
+            assert r * per <= starts[b] + begin and starts[b] + end <= (r + 1) * per
+            tokens += end - begin
+        assert tokens == max(0, min(sum(lens), (r + 1) * per) - r * per)
