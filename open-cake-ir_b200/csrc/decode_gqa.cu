@@ -660,7 +660,7 @@ extern "C" int cake_b200_gqa_decode_destroy(void* handle) {
 // called.
 //
 // All calls share the array and nothing clears it between calls: the plan kernel of a call
-// rewrites the queue, the counters and the work list before the decode kernel of the same call
+// rewrites the counters and the work list before the decode kernel of the same call
 // reads them, and a partial result is read only after the same call has written it, so stale
 // contents are never consumed and nothing needs to start at zero.  Two calls that overlap on the
 // GPU (different streams, or different host threads) race on it -- serialise them.
