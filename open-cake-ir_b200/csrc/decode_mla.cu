@@ -462,6 +462,8 @@ mla_decode_kernel(const Params p) {
 // One CTA per (sequence, head): merges the chunks.  128 threads x 4 dims.
 __global__ void __launch_bounds__(128)
 mla_reduce_kernel(const Params p) {
+  // launched as a programmatic dependent of the decode kernel: resident early, reads after it has completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head = blockIdx.x, b = blockIdx.y;
   const int d = threadIdx.x * 4;
   const int len = seq_len(p, b);
@@ -574,7 +576,21 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
   mla::mla_plan_kernel<<<1, 1024, 0, s>>>(p);
   mla::mla_decode_kernel<<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
-  mla::mla_reduce_kernel<<<dim3(p.heads, p.batch), 128, 0, s>>>(p);
+  {
+    // The reduce grid is a programmatic dependent of the decode grid, which takes its launch latency
+    // off the end of the operator.
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(p.heads, p.batch);
+    config.blockDim = dim3(128);
+    config.stream = s;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&config, mla::mla_reduce_kernel, p);
+    if (err != cudaSuccess) return int(err);
+  }
   return int(cudaGetLastError());
 }
 
