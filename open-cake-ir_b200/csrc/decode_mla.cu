@@ -72,7 +72,7 @@ struct Params {
   float* lse;             // [B, H]
   float* part_o;          // [slots, H, 512]   slot = worker + sequence (see mla_plan_kernel)
   float* part_lse;        // [slots, H]
-  int* tile_prefix;       // [B+1] 32-token tiles before sequence b, written by the plan kernel
+  int* tile_prefix;       // [B+1] work units (tiles + start-up shares) before sequence b, written by the plan kernel
   int* status;
   int batch, heads, page_size, workers;
 };
@@ -136,17 +136,20 @@ __device__ __forceinline__ void load_tile(const Params& p, long long my_slot, ui
   }
 }
 
-// The tiles of all sequences, in order, form one list; worker w (of `workers`) takes the w-th of
-// `workers` equal consecutive ranges of it, so every SM has the same number of tiles whatever the
-// lengths are, and a sequence is cut only where a range ends.  A (worker, sequence) pair that
-// meets writes one partial result; along the list both indices only grow, so worker + sequence
-// numbers the pairs uniquely and at most workers + batch - 1 slots are needed.
-__device__ __forceinline__ int tiles_per_worker(const Params& p) {
+// The work of all sequences, in order, forms one list of units: kSeqCost units for a sequence's
+// start-up and write-out (Q into tensor memory, the partial result out: about ten tiles' worth of
+// time), then one unit per 32-token tile.  Worker w (of `workers`) takes the w-th of `workers` equal
+// consecutive ranges of the list, so every SM has the same amount of work whatever the lengths
+// are, and a sequence is cut only where a range ends.  A (worker, sequence) pair that meets over at
+// least one tile writes one partial result; along the list both indices only grow, so worker +
+// sequence numbers the pairs uniquely and at most workers + batch - 1 slots are needed.
+constexpr int kSeqCost = 10;
+__device__ __forceinline__ int units_per_worker(const Params& p) {
   const int total = p.tile_prefix[p.batch];
   return total > 0 ? (total + p.workers - 1) / p.workers : 1;
 }
 
-// One CTA: tile_prefix[b] = tiles before sequence b (exclusive scan), tile_prefix[B] = all tiles.
+// One CTA: tile_prefix[b] = units before sequence b (exclusive scan), tile_prefix[B] = all units.
 __global__ void __launch_bounds__(1024)
 mla_plan_kernel(const Params p) {
   __shared__ int sums[32];
@@ -154,7 +157,8 @@ mla_plan_kernel(const Params p) {
   int before = 0;
   for (int base = 0; base < p.batch; base += 1024) {
     const int b = base + threadIdx.x;
-    const int n = b < p.batch ? (seq_len(p, b) + kTile - 1) / kTile : 0;
+    const int tiles = b < p.batch ? (seq_len(p, b) + kTile - 1) / kTile : 0;
+    const int n = tiles > 0 ? tiles + kSeqCost : 0;
     int batch_total;
     const int mine = before + cta1024_exclusive_scan(n, sums, batch_total);
     if (b < p.batch) p.tile_prefix[b] = mine;
@@ -168,7 +172,7 @@ mla_decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const int head_blocks = (p.heads + kHeads - 1) / kHeads;
   const int dq = blockIdx.x % kDimSplit, hb = (blockIdx.x / kDimSplit) % head_blocks, worker = blockIdx.x / (kDimSplit * head_blocks);
-  const int per_worker = tiles_per_worker(p);
+  const int per_worker = units_per_worker(p);
   const int range_begin = worker * per_worker, range_end = min(p.tile_prefix[p.batch], range_begin + per_worker);
   if (range_begin >= range_end) return;            // the whole CTA leaves together
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -191,9 +195,11 @@ mla_decode_kernel(const Params p) {
     if (p.tile_prefix[mid] <= at) lo = mid; else hi = mid;
     b = lo;
   }
-  const int first_tile = at - p.tile_prefix[b];
-  const int tiles = min(p.tile_prefix[b + 1], range_end) - at;
-  at += tiles;
+  const int upto = min(p.tile_prefix[b + 1], range_end);        // this range holds units [at, upto) of sequence b
+  const int first_tile = max(at - p.tile_prefix[b] - kSeqCost, 0);
+  const int tiles = upto - p.tile_prefix[b] - kSeqCost - first_tile;
+  at = upto;
+  if (tiles <= 0) continue;                        // only (part of) the sequence's start-up share fell into this range
   const int len = seq_len(p, b);
   const int begin = first_tile * kTile;
   const int end = min(len, begin + tiles * kTile);
@@ -474,8 +480,8 @@ mla_reduce_kernel(const Params p) {
     return;
   }
   // the partial results of sequence b: one per worker whose range holds some of its tiles
-  const int per_worker = tiles_per_worker(p);
-  const int first_worker = p.tile_prefix[b] / per_worker, last_worker = (p.tile_prefix[b + 1] - 1) / per_worker;
+  const int per_worker = units_per_worker(p);
+  const int first_worker = (p.tile_prefix[b] + kSeqCost) / per_worker, last_worker = (p.tile_prefix[b + 1] - 1) / per_worker;
   float mm = -INFINITY;
   for (int w = first_worker; w <= last_worker; ++w) mm = fmaxf(mm, p.part_lse[size_t(w + b) * p.heads + head]);
   float total = 0.f;

@@ -13,11 +13,14 @@ import random
 import pytest
 
 
+SEQ_COST = 10      # units charged at the start of a sequence (kSeqCost)
+
+
 def mla_segments(lens, workers, tile=32):
     tiles = [(n + tile - 1) // tile for n in lens]
     prefix = [0]
     for t in tiles:
-        prefix.append(prefix[-1] + t)
+        prefix.append(prefix[-1] + (t + SEQ_COST if t else 0))
     total = prefix[-1]
     per = (total + workers - 1) // workers if total > 0 else 1
     segments = []
@@ -32,10 +35,13 @@ def mla_segments(lens, workers, tile=32):
                 else:
                     hi = mid
             b = lo
-            n = min(prefix[b + 1], stop) - at
-            segments.append((w, b, at - prefix[b], n))
-            at += n
-    return segments, prefix, per
+            upto = min(prefix[b + 1], stop)
+            first = max(at - prefix[b] - SEQ_COST, 0)
+            n = upto - prefix[b] - SEQ_COST - first
+            at = upto
+            if n > 0:
+                segments.append((w, b, first, n))
+    return segments, prefix, per, tiles
 
 
 @pytest.mark.parametrize("seed", range(6))
@@ -44,25 +50,25 @@ def test_mla_ranges_cover_every_tile_once_and_slots_are_unique(seed):
     batch = rng.choice([1, 2, 7, 32, 100])
     lens = [rng.choice([0, 1, 31, 32, 33, 500, 4097, rng.randrange(0, 9000)]) for _ in range(batch)]
     workers = rng.choice([1, 3, 37, 64])
-    segments, prefix, per = mla_segments(lens, workers)
+    segments, prefix, per, tiles = mla_segments(lens, workers)
     covered = {}
     slots = set()
     for w, b, first, n in segments:
-        assert n > 0 and first + n <= prefix[b + 1] - prefix[b]
+        assert n > 0 and first + n <= tiles[b]
         for t in range(first, first + n):
             assert (b, t) not in covered
             covered[(b, t)] = w
         slot = w + b
         assert slot not in slots and slot < workers + batch
         slots.add(slot)
-    assert len(covered) == prefix[-1]
+    assert len(covered) == sum(tiles)
     # the reduce kernel finds a sequence's partial results from the prefix alone
     for b, n in enumerate(lens):
         if n == 0:
             continue
-        first_w, last_w = prefix[b] // per, (prefix[b + 1] - 1) // per
+        first_w, last_w = (prefix[b] + SEQ_COST) // per, (prefix[b + 1] - 1) // per
         assert {w + b for w in range(first_w, last_w + 1)} == {w + bb for w, bb, _, _ in segments if bb == b}
-    # equal shares: no worker has more than `per` tiles
+    # equal shares: no worker has more than `per` units (tiles + a start-up share per sequence start)
     load = {}
     for w, _, _, n in segments:
         load[w] = load.get(w, 0) + n
