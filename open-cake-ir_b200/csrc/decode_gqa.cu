@@ -56,7 +56,8 @@ struct Params {
   int4* items;                   // [capacity] pieces of sequences in token order, written by the plan kernel:
                                  //   x = b | (pieces of b << 16), y = first token, z = list index of b's first piece, w = end token
   int* item_page;                // [capacity] kv_indptr[b] of the piece
-  int* range_first;              // [ranges + 1] list index of the first piece of each token range
+  int* range_first;              // [ranges] list index of the first piece of each range
+  int* range_count;              // [ranges] pieces of each range
   int* ctrl;                     // [0] work queue cursor, [1] number of entries of `items`
   int* done;                     // [B, Hkv] finished items
   int* status;                   // library status word (may be null)
@@ -124,60 +125,58 @@ __device__ __forceinline__ void load_half(const __nv_bfloat16* __restrict__ cach
   }
 }
 
-// One CTA: cuts the list of all tokens into p.ranges equal ranges (a multiple of the 16-token
-// tile each) and lists the pieces of sequences they hold, in token order, so that the pieces of a
-// range, and the pieces of a sequence, are consecutive entries.  Also resets the counters and writes
-// the results of empty sequences (zeros, lse = -inf), which no piece covers.
+// One CTA: cuts the work of the launch into p.ranges equal ranges and lists the pieces of
+// sequences they hold, in order, so that the pieces of a range, and the pieces of a sequence, are
+// consecutive entries.  Work is counted in token units: kPieceCost units for the start of a sequence
+// (a range that holds the start of another sequence pays one more merge of its two warps, partial
+// result, fence and counter: about 4 us, the time of ~32 tokens), then one unit per token.  Also
+// resets the counters and writes the results of empty sequences (zeros, lse = -inf), which no
+// piece covers.
+constexpr int kPieceCost = 32;
 __global__ void __launch_bounds__(1024)
 gqa_plan_kernel(const Params p) {
   __shared__ long long sums64[32];
   __shared__ int sums32[32];
   const int tid = threadIdx.x;
   if (tid == 0 && p.status) *p.status = 0;
+  for (int r = tid; r < p.ranges; r += 1024) { p.range_first[r] = 0x7fffffff; p.range_count[r] = 0; }
   const int len0 = tid < p.batch ? seq_len(p, tid) : 0;              // the first 1024 lengths stay in registers
-  long long mine = len0, all_tokens = 0;
-  for (int b = tid + 1024; b < p.batch; b += 1024) mine += seq_len(p, b);
-  cta1024_exclusive_scan(mine, sums64, all_tokens);
-  const long long per = max(16LL, (((all_tokens + p.ranges - 1) / p.ranges) + 15) & ~15LL);
+  long long mine = len0 > 0 ? len0 + kPieceCost : 0, all_units = 0;
+  for (int b = tid + 1024; b < p.batch; b += 1024) { const int n = seq_len(p, b); mine += n > 0 ? n + kPieceCost : 0; }
+  cta1024_exclusive_scan(mine, sums64, all_units);                    // (its barriers also publish the defaults above)
+  const long long per = max(16LL, (((all_units + p.ranges - 1) / p.ranges) + 15) & ~15LL);
 
-  int entries = 0;
-  for (int pass = 0; pass < 2; ++pass) {        // count, then write
-    long long tokens_before = 0;
-    int entries_before = 0;
-    for (int base = 0; base < p.batch; base += 1024) {
-      const int b = base + tid;
-      const int len = base == 0 ? len0 : (b < p.batch ? seq_len(p, b) : 0);
-      long long batch_tokens;
-      const long long start = tokens_before + cta1024_exclusive_scan((long long)len, sums64, batch_tokens);
-      const int first_range = int(start / per);
-      const int n = len > 0 ? int((start + len - 1) / per) - first_range + 1 : 0;
-      int batch_entries;
-      const int first = entries_before + cta1024_exclusive_scan(n, sums32, batch_entries);
-      if (pass == 1 && b < p.batch) {
-        const int page_base = p.kv_indptr[b];
-        for (int k = 0; k < n; ++k) {
-          const long long range_start = (long long)(first_range + k) * per;
-          const long long piece_begin = max(start, range_start), piece_end = min(start + len, range_start + per);
-          p.items[first + k] = make_int4(b | (n << 16), int(piece_begin - start), first, int(piece_end - start));
-          p.item_page[first + k] = page_base;
-          if (piece_begin == range_start) p.range_first[first_range + k] = first + k;
-        }
-        for (int h = 0; h < p.hkv; ++h) p.done[size_t(b) * p.hkv + h] = 0;
-        if (len == 0) {
-          for (int h = 0; h < p.hq; ++h) {
-            p.lse[size_t(b) * p.hq + h] = -INFINITY;
-            for (int d = 0; d < kD; ++d) p.out[(size_t(b) * p.hq + h) * kD + d] = __float2bfloat16(0.f);
-          }
+  long long units_before = 0;
+  int entries_before = 0;
+  for (int base = 0; base < p.batch; base += 1024) {
+    const int b = base + tid;
+    const int len = base == 0 ? len0 : (b < p.batch ? seq_len(p, b) : 0);
+    long long batch_units;
+    const long long start = units_before + cta1024_exclusive_scan((long long)(len > 0 ? len + kPieceCost : 0), sums64, batch_units) + kPieceCost;
+    const int first_range = int(start / per);                          // `start`: where the sequence's tokens begin
+    const int n = len > 0 ? int((start + len - 1) / per) - first_range + 1 : 0;
+    int batch_entries;
+    const int first = entries_before + cta1024_exclusive_scan(n, sums32, batch_entries);
+    if (b < p.batch) {
+      const int page_base = p.kv_indptr[b];
+      for (int k = 0; k < n; ++k) {
+        const long long range_start = (long long)(first_range + k) * per;
+        const long long piece_begin = max(start, range_start), piece_end = min(start + len, range_start + per);
+        p.items[first + k] = make_int4(b | (n << 16), int(piece_begin - start), first, int(piece_end - start));
+        p.item_page[first + k] = page_base;
+        atomicMin(p.range_first + first_range + k, first + k);
+        atomicAdd(p.range_count + first_range + k, 1);
+      }
+      for (int h = 0; h < p.hkv; ++h) p.done[size_t(b) * p.hkv + h] = 0;
+      if (len == 0) {
+        for (int h = 0; h < p.hq; ++h) {
+          p.lse[size_t(b) * p.hq + h] = -INFINITY;
+          for (int d = 0; d < kD; ++d) p.out[(size_t(b) * p.hq + h) * kD + d] = __float2bfloat16(0.f);
         }
       }
-      tokens_before += batch_tokens;
-      entries_before += batch_entries;
     }
-    if (pass == 0) {
-      entries = entries_before;
-      for (int r = tid; r <= p.ranges; r += 1024) p.range_first[r] = entries;     // ranges past the last token hold nothing
-      __syncthreads();
-    }
+    units_before += batch_units;
+    entries_before += batch_entries;
   }
 }
 
@@ -284,9 +283,9 @@ gqa_decode_kernel(const Params p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // Items are numbered piece * Hkv + KV head; this pair's run from idx up to (not including) total.
   int idx = 0, total = 0;
-  if (active) {
+  if (active && p.range_count[range_id] > 0) {
     idx = p.range_first[range_id] * p.hkv + kvh_mine;
-    total = p.range_first[range_id + 1] * p.hkv;
+    total = (p.range_first[range_id] + p.range_count[range_id]) * p.hkv;
   }
   int4 rec = make_int4(0, 0, 0, 0);
   int page_base = 0;
@@ -519,11 +518,11 @@ inline size_t entries_for(const cake_b200_gqa_decode_config& c, int sms) {
 }
 
 // Scratch layout shared by the two entry points (offsets from a 256-byte aligned base):
-//   done [B*Hkv] int | items [entries] int4 | item_page [entries] int | range_first [ranges+1] int |
+//   done [B*Hkv] int | items [entries] int4 | item_page [entries] int | range_first [ranges] int | range_count [ranges] int |
 //   part_o [entries*Hq*D] f32 | part_lse [entries*Hq] f32
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 inline size_t scratch_bytes(const cake_b200_gqa_decode_config& c, size_t entries) {
-  return align256(size_t(c.batch) * c.num_kv_heads * sizeof(int)) + align256(entries * sizeof(int4)) + 2 * align256((entries + 1) * sizeof(int)) +
+  return align256(size_t(c.batch) * c.num_kv_heads * sizeof(int)) + align256(entries * sizeof(int4)) + 3 * align256((entries + 1) * sizeof(int)) +
          align256(entries * c.num_qo_heads * kD * sizeof(float)) + align256(entries * c.num_qo_heads * sizeof(float));
 }
 inline void carve_scratch(Params& p, uint8_t* base) {
@@ -534,7 +533,9 @@ inline void carve_scratch(Params& p, uint8_t* base) {
   base += align256(entries * sizeof(int4));
   p.item_page = reinterpret_cast<int*>(base);
   base += align256((entries + 1) * sizeof(int));
-  p.range_first = reinterpret_cast<int*>(base);          // ranges + 1 <= entries + 1
+  p.range_first = reinterpret_cast<int*>(base);          // ranges <= entries
+  base += align256((entries + 1) * sizeof(int));
+  p.range_count = reinterpret_cast<int*>(base);
   base += align256((entries + 1) * sizeof(int));
   p.part_o = reinterpret_cast<float*>(base);
   base += align256(entries * p.hq * kD * sizeof(float));

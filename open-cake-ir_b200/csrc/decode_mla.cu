@@ -143,7 +143,7 @@ __device__ __forceinline__ void load_tile(const Params& p, long long my_slot, ui
 // are, and a sequence is cut only where a range ends.  A (worker, sequence) pair that meets over at
 // least one tile writes one partial result; along the list both indices only grow, so worker +
 // sequence numbers the pairs uniquely and at most workers + batch - 1 slots are needed.
-constexpr int kSeqCost = 10;
+constexpr int kSeqCost = 14;
 __device__ __forceinline__ int units_per_worker(const Params& p) {
   const int total = p.tile_prefix[p.batch];
   return total > 0 ? (total + p.workers - 1) / p.workers : 1;

@@ -75,27 +75,29 @@ def test_mla_ranges_cover_every_tile_once_and_slots_are_unique(seed):
     assert max(load.values(), default=0) <= per
 
 
+PIECE_COST = 32    # token units charged at the start of a sequence (kPieceCost)
+
+
 def gqa_pieces(lens, ranges):
-    total = sum(lens)
+    total = sum(n + PIECE_COST for n in lens if n > 0)
     per = max(16, (((total + ranges - 1) // ranges) + 15) & ~15)
-    items, range_first, start = [], None, 0
-    counts = []
-    for n in lens:
-        first_range = start // per
-        counts.append((start + n - 1) // per - first_range + 1 if n > 0 else 0)
-        start += n
-    range_first = [sum(counts)] * (ranges + 1)
-    start = 0
+    items, range_first, range_count = [], [None] * ranges, [0] * ranges
+    before = 0
     for b, n in enumerate(lens):
+        if n == 0:
+            continue
+        start = before + PIECE_COST                      # where the sequence's tokens begin, in units
+        first_range, count = start // per, (start + n - 1) // per - start // per + 1
         first = len(items)
-        for k in range(counts[b]):
-            range_start = (start // per + k) * per
+        for k in range(count):
+            range_start = (first_range + k) * per
             begin, end = max(start, range_start), min(start + n, range_start + per)
-            if begin == range_start:
-                range_first[start // per + k] = len(items)
-            items.append((b, counts[b], begin - start, first, end - start))
-        start += n
-    return items, range_first, per
+            r = first_range + k
+            range_first[r] = len(items) if range_first[r] is None else min(range_first[r], len(items))
+            range_count[r] += 1
+            items.append((b, count, begin - start, first, end - start))
+        before += n + PIECE_COST
+    return items, range_first, range_count, per
 
 
 @pytest.mark.parametrize("seed", range(5))
@@ -103,7 +105,7 @@ def test_gqa_ranges_partition_the_token_list(seed):
     rng = random.Random(100 + seed)
     lens = [rng.choice([0, 1, 15, 16, 17, 700, 4096, rng.randrange(0, 5000)]) for _ in range(rng.choice([1, 5, 64]))]
     ranges = rng.choice([1, 18, 148, 1184])
-    items, range_first, per = gqa_pieces(lens, ranges)
+    items, range_first, range_count, per = gqa_pieces(lens, ranges)
     assert per % 16 == 0 and len(items) <= ranges + len(lens)
     # pieces of a sequence: consecutive entries, tiling it exactly
     for b, n in enumerate(lens):
@@ -114,16 +116,11 @@ def test_gqa_ranges_partition_the_token_list(seed):
             assert count == len(mine) and first == mine[0][0] and begin == pos and end > begin
             pos = end
         assert pos == n
-    # pieces of a range: entries range_first[r] .. range_first[r+1], all inside the range, `per` tokens unless it is the last
-    starts = [0]
-    for n in lens:
-        starts.append(starts[-1] + n)
-    assert range_first[0] == 0 or sum(lens) == 0
+    # pieces of a range: consecutive entries, every entry in exactly one range, no range above its share
+    seen = []
     for r in range(ranges):
-        lo, hi = range_first[r], range_first[r + 1]
-        assert lo <= hi
-        tokens = 0
-        for b, _, begin, _, end in items[lo:hi]:
-            assert r * per <= starts[b] + begin and starts[b] + end <= (r + 1) * per
-            tokens += end - begin
-        assert tokens == max(0, min(sum(lens), (r + 1) * per) - r * per)
+        if range_count[r]:
+            seen.extend(range(range_first[r], range_first[r] + range_count[r]))
+            units = sum(end - begin for _, _, begin, _, end in items[range_first[r]:range_first[r] + range_count[r]])
+            assert units <= per
+    assert seen == list(range(len(items)))
