@@ -54,6 +54,7 @@ extern "C" int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b20
   p.out = buffers[4];
   h->status = static_cast<int*>(buffers[5]);
   p.status = h->status;
+  p.queue = h->status + 4;               // work-item counter, inside the 256-byte status block
   const long long items = ((m + gemm::kBM - 1) / gemm::kBM) * ((n + gemm::kBN - 1) / gemm::kBN);
   const int sms = sm_count(device);
   h->grid = int(items < sms ? items : sms);
@@ -72,7 +73,7 @@ extern "C" int cake_b200_block_scaled_gemm_launch(void* handle, void* cuda_strea
   CAKE_CUDA_OK(cudaGetDevice(&device));
   if (device != h->device) return kErrWrongDevice;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
-  CAKE_CUDA_OK(cudaMemsetAsync(h->status, 0, sizeof(int), stream));
+  CAKE_CUDA_OK(cudaMemsetAsync(h->status, 0, 8 * sizeof(int), stream));     // status word and work-item counter
   gemm::gemm_fp8_kernel<gemm::kDense><<<h->grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(h->map_a, h->map_b, h->params);
   return int(cudaGetLastError());
 }

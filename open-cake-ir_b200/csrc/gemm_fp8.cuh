@@ -21,6 +21,8 @@
 // 4-stage TMA ring (128-byte swizzle, one elected producer thread); the MMA is issued by one
 // elected thread of a second warp.  Work items are (group, n tile, m tile) with the m tile
 // fastest, so CTAs that share a weight tile run at the same time and the second reader hits L2.
+// Items either go round the CTAs in turn or are drawn from a device counter by the TMA warp, which
+// hands them to the other roles through a four-slot ring (Params::queue).
 #pragma once
 #include "common.cuh"
 
@@ -54,6 +56,7 @@ constexpr int kEpilogueRegs = 232;
 static_assert(kControlWarps * 32 * kControlRegs + kEpilogueWarps * 32 * kEpilogueRegs <= (65536 / kThreads / 8 * 8) * kThreads,
               "setmaxnreg budget exceeds the registers the launch allocates");
 constexpr int kMaxGroups = 512;
+constexpr int kItemSlots = 4;
 
 enum Mode : int {
   kDense = 0,        // C bf16 [M, N]
@@ -79,6 +82,7 @@ struct Params {
   const float* row_weight;     // kDown: [row_capacity] route weight per sorted row
   int split_act;               // kGateUp: 1 = also write the residual (lo) term
   int* status;                 // device status word (0 = ok)
+  int* queue;                  // device counter, 0 at launch: work items are drawn from it (null: item i goes to CTA i mod grid)
 };
 
 struct Shared {
@@ -86,6 +90,8 @@ struct Shared {
   uint64_t empty[kStages];
   uint64_t tmem_full[kTmemStages];
   uint64_t tmem_empty[kTmemStages];
+  uint64_t item_full[kItemSlots], item_empty[kItemSlots];   // hand-over of drawn work items from the TMA warp to the other roles
+  int item_q[kItemSlots];
   uint32_t tmem_base;
   int abort_flag;
   int tile_prefix[kMaxGroups + 1];     // m tiles before group g
@@ -132,6 +138,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
     for (int s = 0; s < kTmemStages; ++s) { mbar_init(&sh->tmem_full[s], 1); mbar_init(&sh->tmem_empty[s], kEpilogueWarps); }
+    for (int s = 0; s < kItemSlots; ++s) { mbar_init(&sh->item_full[s], 1); mbar_init(&sh->item_empty[s], 1 + kEpilogueWarps); }
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -173,10 +180,26 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tma_prefetch_descriptor(&map_a);
       tma_prefetch_descriptor(&map_b);
       const uint64_t keep = l2_policy_evict_last();    // activations: re-read by every n tile
-      uint32_t it = 0;
+      // Work items.  With a queue, this thread draws them (the first is the CTA's index, every later
+      // one comes from the device counter, asked for one item ahead) and hands each to the MMA and
+      // epilogue warps through a small ring, so that an SM that runs slower simply takes fewer
+      // items; without one, item i belongs to CTA i mod grid.
+      uint32_t it = 0, k = 0;
       bool ok = true;
       Item item;
-      for (int g = blockIdx.x; ok && locate(sh, p, n_tiles, g, &item); g += gridDim.x) {
+      int g = blockIdx.x;
+      while (ok) {
+        const bool valid = locate(sh, p, n_tiles, g, &item);
+        int drawn = g + int(gridDim.x);
+        if (p.queue) {
+          const int slot = k % kItemSlots;
+          ok = mbar_wait(&sh->item_empty[slot], ((k / kItemSlots) & 1) ^ 1, abort_flag, p.status, kStatusWaitFlag);
+          if (!ok) break;
+          sh->item_q[slot] = valid ? g : -1;
+          mbar_arrive(&sh->item_full[slot]);
+          if (valid) drawn = int(gridDim.x) + atomicAdd(p.queue, 1);
+        }
+        if (!valid) break;
         const int b_row0 = item.group * p.b_rows_per_group;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kStages;
@@ -196,16 +219,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tma_load_2d(b_dst, &map_b, b_col * kBK, b_row0 + item.n_tile * kBN, &sh->full[s]);
           }
         }
+        g = drawn;
+        ++k;
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------------------
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc(0 /* e4m3 */, kBM, kBN);
-      uint32_t it = 0;
+      uint32_t it = 0, k = 0;
       bool ok = true;
       Item item;
-      for (int g = blockIdx.x; ok && locate(sh, p, n_tiles, g, &item); g += gridDim.x) {
+      for (int g = blockIdx.x; ok; g += gridDim.x, ++k) {
+        if (p.queue) {                 // the k-th item of this CTA, as drawn by the TMA warp
+          const int slot = k % kItemSlots;
+          ok = mbar_wait(&sh->item_full[slot], (k / kItemSlots) & 1, abort_flag, p.status, kStatusWaitFlag);
+          if (!ok) break;
+          g = sh->item_q[slot];
+          mbar_arrive(&sh->item_empty[slot]);
+          if (g < 0) break;
+        }
+        if (!locate(sh, p, n_tiles, g, &item)) break;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const int t = it % kTmemStages;
@@ -241,11 +275,21 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int seg_col0 = (MODE == kGateUp) ? cg * 64 : cg * 128;
     const int seg_col1 = (MODE == kGateUp) ? 128 + cg * 64 : cg * 128 + 64;
     const int sfb_rows = p.b_rows_per_group / 128;
-    uint32_t it = 0;
+    uint32_t it = 0, k = 0;
     int parity = 0;
     bool ok = true;
     Item item;
-    for (int g = blockIdx.x; ok && locate(sh, p, n_tiles, g, &item); g += gridDim.x, parity ^= 1) {
+    for (int g = blockIdx.x; ok; g += gridDim.x, parity ^= 1, ++k) {
+      if (p.queue) {                   // the k-th item of this CTA, as drawn by the TMA warp
+        const int slot = k % kItemSlots;
+        ok = mbar_wait(&sh->item_full[slot], (k / kItemSlots) & 1, abort_flag, p.status, kStatusWaitFlag);
+        if (!ok) break;
+        g = sh->item_q[slot];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->item_empty[slot]);
+        if (g < 0) break;
+      }
+      if (!locate(sh, p, n_tiles, g, &item)) break;
       const int row = item.row0 + r;
       const int row_c = min(row, p.row_capacity - 1);
       int sfb_row0, sfb_row1;
