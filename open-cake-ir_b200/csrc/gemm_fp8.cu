@@ -1,7 +1,6 @@
 // Dense block-scaled FP8 GEMM entry points (C ABI) on top of the shared tcgen05 core.
 #include "gemm_fp8.cuh"
 #include "../../include/cake_b200.h"
-#include <cstdlib>
 #include <new>
 
 namespace cake {
@@ -58,9 +57,6 @@ extern "C" int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b20
   const long long items = ((m + gemm::kBM - 1) / gemm::kBM) * ((n + gemm::kBN - 1) / gemm::kBN);
   const int sms = sm_count(device);
   h->grid = int(items < sms ? items : sms);
-#if CAKE_GEMM_PROBE
-  if (const char* g = getenv("CAKE_PROBE_GRID")) h->grid = atoi(g);
-#endif
   *handle_out = h;
   return 0;
 }
