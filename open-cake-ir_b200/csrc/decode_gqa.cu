@@ -58,7 +58,6 @@ struct Params {
   int* item_page;                // [capacity] kv_indptr[b] of the piece
   int* range_first;              // [ranges] list index of the first piece of each range
   int* range_count;              // [ranges] pieces of each range
-  int* ctrl;                     // [0] work queue cursor, [1] number of entries of `items`
   int* done;                     // [B, Hkv] finished items
   int* status;                   // library status word (may be null)
   int batch, hq, hkv, page_size, capacity, ranges;
@@ -210,7 +209,7 @@ __device__ __forceinline__ void merge_chunks_t(const Params& p, int b, int kvh, 
 #pragma unroll
       for (int k = 0; k < NF; ++k) v[i][k] = __ldcg(src + sub + L * k);
     }
-    float m_new = mm;                   // every chunk holds a token, so its lse is finite
+    float m_new = mm;                   // every piece holds a token, so its lse is finite
 #pragma unroll
     for (int i = 0; i < BATCH; ++i) m_new = fmaxf(m_new, ls[i]);
     const float rescale = exp2f(mm - m_new);            // 0 on the first batch
