@@ -13,7 +13,7 @@ import random
 import pytest
 
 
-SEQ_COST = 10      # units charged at the start of a sequence (kSeqCost)
+SEQ_COST = 14      # units charged at the start of a sequence (kSeqCost)
 
 
 def mla_segments(lens, workers, tile=32):
