@@ -22,7 +22,9 @@
  * shape-specialised source: a per-operator config struct passed to `create` (the reference
  * bakes shapes into emitted code), and a device status word at the start of the workspace
  * that a kernel sets when one of its bounded waits runs out (read it with
- * cake_b200_read_status after synchronising the stream).
+ * cake_b200_read_status after synchronising the stream).  The first 256 bytes of a workspace
+ * are the library's (the status word, then the counters its kernels draw work items from);
+ * `launch` clears what it uses on the stream, so a workspace needs no initialisation.
  *
  * Return values: 0 on success; a cudaError_t value; 10000 + CUresult for driver errors
  * (the reference's convention, native-gemm-bias.txt:192,199); 20001.. for this library's
