@@ -25,6 +25,10 @@
  * cake_b200_read_status after synchronising the stream).  The first 256 bytes of a workspace
  * are the library's (the status word, then the counters its kernels draw work items from);
  * `launch` clears what it uses on the stream, so a workspace needs no initialisation.
+ * Workspace alignment: 4 bytes for the decode operators and the dense GEMM (16 there), which
+ * align what follows the status block themselves inside the size they ask for; 256 bytes for
+ * the MoE layer, whose workspace holds TMA-addressed tiles (create returns
+ * CAKE_B200_ERR_BAD_ARGUMENT otherwise).
  *
  * Return values: 0 on success; a cudaError_t value; 10000 + CUresult for driver errors
  * (the reference's convention, native-gemm-bias.txt:192,199); 20001.. for this library's
@@ -70,6 +74,28 @@ typedef struct {
 int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_config* config, void** handle_out);
 int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream);
 int cake_b200_rmsnorm_destroy(void* handle);
+/* RMSNorm takes no workspace, so its kernels report a bounded wait that ran out (a row's bulk copy that never
+ * landed) through a status word inside the library instead: 0, or the code, for the current device since the
+ * library was loaded.  Synchronises `cuda_stream`. */
+int cake_b200_rmsnorm_last_status(void* cuda_stream, int* status_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Residual add + RMSNorm with two outputs.  Replaces the emitted starter of the reference's
+ * `add_rmsnorm_bf16` task (src/open_cake_ir/tasks/add_rmsnorm.py:145-181; definition :66, oracle :131-143):
+ *   z = bf16(delta + residual)  (fp32 add, round to nearest even);  residual_out = z;
+ *   out = bf16( fp32(z) * rsqrt(mean_j fp32(z)^2 + epsilon) * fp32(weight) )
+ * The rounded sum is both what is returned as residual_out (compared bit for bit by the contract) and what is
+ * normalised.  buffers: delta bf16 [rows,width], residual bf16 [rows,width], weight bf16 [width],
+ *          out bf16 [rows,width], residual_out bf16 [rows,width].  width % 8 == 0, width <= 8192.  No workspace.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t rows;
+  int64_t width;
+  float epsilon;
+} cake_b200_add_rmsnorm_config;
+int cake_b200_add_rmsnorm_create(void** buffers, const cake_b200_add_rmsnorm_config* config, void** handle_out);
+int cake_b200_add_rmsnorm_launch(void* handle, void* cuda_stream);
+int cake_b200_add_rmsnorm_destroy(void* handle);
 
 /* ------------------------------------------------------------------------------------------
  * Block-scaled FP8 GEMM.  Replaces the emitted block-scaled GEMM
@@ -106,6 +132,41 @@ typedef struct {
 int cake_b200_moe_routing_create(void** buffers, const cake_b200_routing_config* config, void** handle_out);
 int cake_b200_moe_routing_launch(void* handle, void* cuda_stream);
 int cake_b200_moe_routing_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * DeepSeek-V4 MoE gate.  Replaces the emitted program of the reference's `deepseek_v4_moe_gate_fp32` task
+ * (contract src/open_cake_ir/tasks/deepseek_v4/workload.py:46-108, oracle :190-201;
+ * contracts/workloads/deepseek-v4-moe-gate-fp32-triton-b200-v1.json):
+ *   score = fp32(sqrt(log1p(exp(router_logits)))); expert_ids = the top_k of score + selection_bias, descending;
+ *   weights = fp32(route_scale * score[expert_ids] / sum(score[expert_ids])).  The bias enters the choice only.
+ * buffers (the contract's order, outputs `weights` then `expert_ids`): router_logits fp32 [T,E],
+ *          selection_bias fp32 [E], weights fp32 [T,top_k], expert_ids int32 [T,top_k].  E <= 512, top_k <= 32.
+ * Equal biased scores, which the contract excludes, go to the lower expert id.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t tokens;
+  int32_t experts, top_k;
+  float route_scale; /* 2.5 in the contract */
+} cake_b200_v4_gate_config;
+int cake_b200_v4_moe_gate_create(void** buffers, const cake_b200_v4_gate_config* config, void** handle_out);
+int cake_b200_v4_moe_gate_launch(void* handle, void* cuda_stream);
+int cake_b200_v4_moe_gate_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * DeepSeek-V4 CSA indexer top-k.  Replaces the emitted program of the reference's
+ * `deepseek_v4_csa_indexer_topk_fp32` task (src/open_cake_ir/tasks/deepseek_v4/workload.py:46-108, oracle :188-189;
+ * contracts/workloads/deepseek-v4-csa-indexer-topk-fp32-triton-b200-v1.json):
+ *   indices[q,:] = positions of the top_k largest index_scores[q,:], in descending score order.
+ * buffers: index_scores fp32 [Q,S], indices int32 [Q,top_k].  S <= 2048 (the contract: S 2048, top_k 1024).
+ * Equal scores, which the contract excludes, order by ascending position.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t rows;
+  int32_t candidates, top_k;
+} cake_b200_topk_config;
+int cake_b200_csa_topk_create(void** buffers, const cake_b200_topk_config* config, void** handle_out);
+int cake_b200_csa_topk_launch(void* handle, void* cuda_stream);
+int cake_b200_csa_topk_destroy(void* handle);
 
 /* ------------------------------------------------------------------------------------------
  * Token permute.  Fixes the order the reference leaves open (atomic reservation judged by ownership,
@@ -223,6 +284,30 @@ int cake_b200_mla_decode_launch(void* handle, void* cuda_stream);
 int cake_b200_mla_decode_destroy(void* handle);
 
 /* ------------------------------------------------------------------------------------------
+ * Sparse MLA decode (DeepSeek-V3.2 sparse attention).  Implements the operator of the reference's
+ * `dsa_attention` contract (contracts/workloads/dsa-attention-sparse-mla-decode-v1.json, validator
+ * src/open_cake_ir/tasks/dsa/contract.py:5-78): for each query row and head, the cache rows named by the
+ * non-negative entries of sparse_indices[t,:] (token-level row numbers page*page_size + offset; -1 = no entry)
+ *   logits = (q_nope . ckv + q_pe . kpe) * sm_scale; out = bf16(softmax over the present entries . ckv);
+ *   no present entry => a row of zeros.
+ * buffers: q_nope bf16 [T,H,512], q_pe bf16 [T,H,64], ckv_cache bf16 [pages,page_size,512],
+ *          kpe_cache bf16 [pages,page_size,64], sparse_indices int32 [T,top_k], output bf16 [T,H,512], workspace.
+ * sm_scale is a number of the contract (0.1352337788608801), not a tensor, so it is part of the config.
+ * The kernel is the paged MLA decode kernel with the page walk replaced by the index list (16 heads of the
+ * contract occupy 16 of its 128 head rows).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t num_tokens;      /* query rows */
+  int64_t num_cache_rows;  /* pages * page_size: indices must be below it (not checked on the device) */
+  int32_t num_qo_heads, head_dim_ckv, head_dim_kpe, top_k;
+  float sm_scale;
+} cake_b200_sparse_mla_decode_config;
+size_t cake_b200_sparse_mla_decode_workspace_bytes(const cake_b200_sparse_mla_decode_config* config);
+int cake_b200_sparse_mla_decode_create(void** buffers, const cake_b200_sparse_mla_decode_config* config, void** handle_out);
+int cake_b200_sparse_mla_decode_launch(void* handle, void* cuda_stream);
+int cake_b200_sparse_mla_decode_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
  * Expert-parallel exchange around the rank-local MoE layer.  The reference holds only the rank-local view
  * (a rank owns experts [local_expert_offset, +local_experts) and other pairs contribute nothing,
  * src/open_cake_ir/tasks/solx_fib/moe.py:139-146); these kernels are the data movement that joins R such ranks.
@@ -237,7 +322,8 @@ int cake_b200_mla_decode_destroy(void* handle);
  *   [world*capacity,H], scales fp32 [H/128,world*capacity], expert_ids int32 and route_weights fp32
  *   [world*capacity,top_k]; 11 returned bf16 [world,capacity,H] (filled by the caller's reverse all-to-all of the
  *   layer's output); 12 output bf16 [T,H] (written by stage 2: partial rows added in rank order in fp32).
- * stages: 0 plan + pack, 1 unpack, 2 reduce.  H % 512 == 0 (packed rows stay 16-byte aligned).
+ * stages: 0 plan + pack, 1 unpack, 2 reduce.  H % 512 == 0 and top_k even: packed rows are moved with 16-byte loads and
+ * stores, so row_bytes must be a multiple of 16; cake_b200_ep_row_bytes returns 0 for any other configuration.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   int64_t tokens;   /* tokens of this rank */

@@ -33,6 +33,10 @@ class RmsNormConfig(Structure):
     _fields_ = [("rows", c_int64), ("width", c_int64), ("epsilon", c_float), ("fused_residual", c_int32)]
 
 
+class AddRmsNormConfig(Structure):
+    _fields_ = [("rows", c_int64), ("width", c_int64), ("epsilon", c_float)]
+
+
 class GemmConfig(Structure):
     _fields_ = [("m", c_int64), ("n", c_int64), ("k", c_int64)]
 
@@ -40,6 +44,14 @@ class GemmConfig(Structure):
 class RoutingConfig(Structure):
     _fields_ = [("tokens", c_int64), ("experts", c_int32), ("top_k", c_int32), ("n_group", c_int32),
                 ("topk_group", c_int32), ("mode", c_int32)]
+
+
+class V4GateConfig(Structure):
+    _fields_ = [("tokens", c_int64), ("experts", c_int32), ("top_k", c_int32), ("route_scale", c_float)]
+
+
+class TopkConfig(Structure):
+    _fields_ = [("rows", c_int64), ("candidates", c_int32), ("top_k", c_int32)]
 
 
 class PermuteConfig(Structure):
@@ -67,18 +79,27 @@ class MlaDecodeConfig(Structure):
                 ("page_size", c_int32), ("max_kv_len", c_int64)]
 
 
+class SparseMlaDecodeConfig(Structure):
+    _fields_ = [("num_tokens", c_int64), ("num_cache_rows", c_int64), ("num_qo_heads", c_int32), ("head_dim_ckv", c_int32),
+                ("head_dim_kpe", c_int32), ("top_k", c_int32), ("sm_scale", c_float)]
+
+
 # operator stem -> (config struct, has a workspace query)
 OPERATORS = {
     "rmsnorm": (RmsNormConfig, False),
+    "add_rmsnorm": (AddRmsNormConfig, False),
     "block_scaled_gemm": (GemmConfig, True),
     "moe_routing": (RoutingConfig, False),
     "moe_permute": (PermuteConfig, False),
+    "v4_moe_gate": (V4GateConfig, False),
+    "csa_topk": (TopkConfig, False),
     "moe": (MoeConfig, True),
     "gqa_decode": (GqaDecodeConfig, True),
     "mla_decode": (MlaDecodeConfig, True),
+    "sparse_mla_decode": (SparseMlaDecodeConfig, True),
 }
 # every symbol include/cake_b200.h declares
-EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
+EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_rmsnorm_last_status", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
             "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit",
             "cake_b200_ep_row_bytes", "cake_b200_ep_exchange_create", "cake_b200_ep_exchange_launch_stage",
             "cake_b200_ep_exchange_destroy"]
@@ -98,6 +119,7 @@ def library() -> ctypes.CDLL:
         lib = ctypes.CDLL(str(LIBRARY_PATH))
         lib.cake_b200_abi_version.restype = c_int
         lib.cake_b200_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
+        lib.cake_b200_rmsnorm_last_status.argtypes = [c_void_p, POINTER(c_int)]
         lib.cake_b200_moe_intermediate.argtypes = [c_void_p, c_int, POINTER(c_void_p)]
         lib.cake_b200_moe_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
         lib.cake_b200_gqa_decode_noalloc.argtypes = [POINTER(c_void_p), POINTER(GqaDecodeConfig), c_void_p]

@@ -16,9 +16,11 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIBRARY = HERE / "libcake_b200.so"
-SOURCES = ("rmsnorm.cu", "gemm_fp8.cu", "moe.cu", "decode_gqa.cu", "decode_mla.cu", "ep.cu", "misc.cu")
-NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-Xptxas", "-v")
+SOURCES = ("rmsnorm.cu", "gemm_fp8.cu", "moe.cu", "routing_v4.cu", "decode_gqa.cu", "decode_mla.cu", "ep.cu", "misc.cu")
+# The architecture selectors are the two the target document (targets/sm_100a_native.json) declares and the
+# only ones: the long form of `-gencode arch=compute_100a,code=sm_100a`.
+ARCH_FLAGS = ("--gpu-architecture=compute_100a", "--gpu-code=sm_100a")
+NVCC_FLAGS = (*ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xptxas", "-v")
 
 
 def _nvcc() -> str:

@@ -610,7 +610,7 @@ extern "C" int cake_b200_gqa_decode_create(void** buffers, const cake_b200_gqa_d
   *handle_out = nullptr;
   int device = 0;
   if (int rc = require_blackwell(&device)) return rc;
-  if (!gqa_config_ok(*config) || !buffers[9]) return kErrBadArgument;
+  if (!gqa_config_ok(*config) || !buffers[9] || (reinterpret_cast<uintptr_t>(buffers[9]) & 3)) return kErrBadArgument;
   auto* h = new (std::nothrow) gqa::Handle;
   if (!h) return int(cudaErrorMemoryAllocation);
   h->device = device;

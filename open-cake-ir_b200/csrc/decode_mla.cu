@@ -75,6 +75,10 @@ struct Params {
   int* tile_prefix;       // [B+1] work units (tiles + start-up shares) before sequence b, written by the plan kernel
   int* status;
   int batch, heads, page_size, workers;
+  // Sparse form (DeepSeek-V3.2 sparse attention): sequence b is the `top_k` cache rows listed in
+  // sparse_indices[b, :] (token-level row numbers page * page_size + offset, -1 = no entry) instead of a page list.
+  const int* sparse_indices;
+  int top_k;
 };
 
 struct Shared {
@@ -91,6 +95,7 @@ struct Shared {
 constexpr size_t kSmemBytes = size_t(kQSmemBytes) + size_t(kStages) * kKvStageBytes + sizeof(Shared) + 1024;
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
+  if (p.sparse_indices) return p.top_k;            // listed entries, some of which may be -1
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
   return pages <= 0 ? 0 : (pages - 1) * p.page_size + p.kv_last_page_len[b];
 }
@@ -119,6 +124,7 @@ __device__ __forceinline__ uint32_t slab_off(int rows, int row, int chunk) {
 __device__ __forceinline__ long long lookup_row(const Params& p, int page_base, int tok0, int len, int loader_tid) {
   const int tok = tok0 + (loader_tid >> 5) * 8 + (loader_tid & 7);
   if (tok >= len) return -1;
+  if (p.sparse_indices) return (long long)__ldg(p.sparse_indices + page_base + tok);      // page_base = b * top_k here
   const int page = __ldg(p.kv_indices + page_base + tok / p.page_size);
   return (long long)page * p.page_size + (tok % p.page_size);
 }
@@ -167,6 +173,7 @@ mla_plan_kernel(const Params p) {
   if (threadIdx.x == 0) p.tile_prefix[p.batch] = before;
 }
 
+template <bool SPARSE>
 __global__ void __launch_bounds__(kThreads, 1)
 mla_decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -233,7 +240,7 @@ mla_decode_kernel(const Params p) {
   cp_async_commit();
   // The first tile goes out while the Q block is in flight (its page lookup is two dependent loads);
   // it is a copy group of its own, so that the barrier below waits for Q only.
-  const int page_base = p.kv_indptr[b];
+  const int page_base = SPARSE ? b * p.top_k : p.kv_indptr[b];
   if (warp < kLoaderWarps) load_tile(p, lookup_row(p, page_base, begin, end, threadIdx.x), kv_addr, threadIdx.x);
   cp_async_commit();
   cp_async_wait<1>();
@@ -367,7 +374,15 @@ mla_decode_kernel(const Params p) {
       // its dependent chains short.
       const int tok0 = begin + i * kTile;
       float t4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (tok0 + kTile <= end) {                     // all but a chunk's last tile
+      if (SPARSE) {                                  // entries of the list may be absent anywhere
+        const int tok = tok0 + lane;
+        const uint32_t present = __ballot_sync(0xffffffffu, tok < end && __ldg(p.sparse_indices + page_base + tok) >= 0);
+#pragma unroll
+        for (int c = 0; c < kTile; ++c) {
+          sc[c] = ((present >> c) & 1u) ? sc[c] * scale2 : -INFINITY;
+          t4[c & 3] = fmaxf(t4[c & 3], sc[c]);
+        }
+      } else if (tok0 + kTile <= end) {              // all but a chunk's last tile
 #pragma unroll
         for (int c = 0; c < kTile; ++c) {
           sc[c] *= scale2;
@@ -387,7 +402,7 @@ mla_decode_kernel(const Params p) {
         tcgen05_fence_after();
       }
       if (i == 0) {
-        m_ref = tmax;                                // finite: the first tile holds a valid token
+        m_ref = tmax;                                // finite: the first tile holds a valid token (sparse: may be -inf)
       } else {
         const bool need = tmax > m_ref + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {         // both warps of a row see the same logits and decide alike
@@ -395,7 +410,7 @@ mla_decode_kernel(const Params p) {
           ok = mbar_wait(&sh->pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
           if (!ok) break;
           tcgen05_fence_after();
-          const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
+          const float alpha = need ? exp2f(m_ref - tmax) : 1.f;      // m_ref = -inf (sparse: nothing present so far) gives 0
           if (need) { m_ref = tmax; l *= alpha; }
 #pragma unroll 1
           for (int c = grp * kOwnCols; c < (grp + 1) * kOwnCols; c += 32) {
@@ -414,7 +429,9 @@ mla_decode_kernel(const Params p) {
 #pragma unroll
       for (int c = 0; c < kTile / 2; c += 2) {
         const float x0 = grp == 0 ? sc[c] : sc[kTile / 2 + c], x1 = grp == 0 ? sc[c + 1] : sc[kTile / 2 + c + 1];
-        const float p0 = exp2f(x0 - m_ref), p1 = exp2f(x1 - m_ref);
+        // sparse: while no entry has been present m_ref is -inf and every logit is -inf: the weights are 0, not NaN
+        const float m_use = (SPARSE && m_ref == -INFINITY) ? 0.f : m_ref;
+        const float p0 = exp2f(x0 - m_use), p1 = exp2f(x1 - m_use);
         s4[(c >> 1) & 3] += p0 + p1;
         split_bf16x2(p0, p1, hi[c >> 1], lo[c >> 1]);
       }
@@ -438,7 +455,7 @@ mla_decode_kernel(const Params p) {
       tcgen05_fence_after();
       const int head = head0 + r;
       const float total = sh->l_part[0][r] + sh->l_part[1][r];
-      const float inv = 1.f / total;
+      const float inv = (SPARSE && total == 0.f) ? 0.f : 1.f / total;        // sparse: no entry present in this range
       const size_t slot = size_t(slot_index) * p.heads + (head < p.heads ? head : 0);
       float* dst = p.part_o + slot * kCkv + dq * kDimsPerCta;
 #pragma unroll 1
@@ -452,7 +469,7 @@ mla_decode_kernel(const Params p) {
             *reinterpret_cast<float4*>(dst + c + k) = make_float4(o[k] * inv, o[k + 1] * inv, o[k + 2] * inv, o[k + 3] * inv);
         }
       }
-      if (dq == 0 && grp == 0 && head < p.heads) p.part_lse[slot] = m_ref + log2f(total);
+      if (dq == 0 && grp == 0 && head < p.heads) p.part_lse[slot] = (SPARSE && total == 0.f) ? -INFINITY : m_ref + log2f(total);
     }
   }
 
@@ -476,7 +493,7 @@ mla_reduce_kernel(const Params p) {
   __nv_bfloat16* out = p.out + (size_t(b) * p.heads + head) * kCkv + d;
   if (len == 0) {
     *reinterpret_cast<uint2*>(out) = make_uint2(0u, 0u);
-    if (threadIdx.x == 0) p.lse[size_t(b) * p.heads + head] = -INFINITY;
+    if (threadIdx.x == 0 && p.lse) p.lse[size_t(b) * p.heads + head] = -INFINITY;
     return;
   }
   // the partial results of sequence b: one per worker whose range holds some of its tiles
@@ -484,6 +501,11 @@ mla_reduce_kernel(const Params p) {
   const int first_worker = (p.tile_prefix[b] + kSeqCost) / per_worker, last_worker = (p.tile_prefix[b + 1] - 1) / per_worker;
   float mm = -INFINITY;
   for (int w = first_worker; w <= last_worker; ++w) mm = fmaxf(mm, p.part_lse[size_t(w + b) * p.heads + head]);
+  if (mm == -INFINITY) {                           // sparse form: every listed entry of the row was absent
+    *reinterpret_cast<uint2*>(out) = make_uint2(0u, 0u);
+    if (threadIdx.x == 0 && p.lse) p.lse[size_t(b) * p.heads + head] = -INFINITY;
+    return;
+  }
   float total = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int w = first_worker; w <= last_worker; ++w) {
@@ -495,12 +517,13 @@ mla_reduce_kernel(const Params p) {
   }
   const float inv = 1.f / total;
   *reinterpret_cast<uint2*>(out) = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
-  if (threadIdx.x == 0) p.lse[size_t(b) * p.heads + head] = mm + log2f(total);
+  if (threadIdx.x == 0 && p.lse) p.lse[size_t(b) * p.heads + head] = mm + log2f(total);
 }
 
 struct Handle {
   int device;
   Params p;
+  float sm_scale;            // sparse form: the scale is a configuration number, copied into the workspace at launch
 };
 
 constexpr int kMaxWorkers = 128;                           // workers the scratch is sized for (SMs / 2 per head block)
@@ -552,8 +575,14 @@ extern "C" int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_d
   p.batch = int(config->batch);
   p.heads = config->num_qo_heads;
   p.page_size = config->page_size;
-  p.status = static_cast<int*>(buffers[10]);
+  p.sparse_indices = nullptr;
+  p.top_k = 0;
+  if (reinterpret_cast<uintptr_t>(buffers[10]) & 3) { delete h; return kErrBadArgument; }
+  p.status = static_cast<int*>(buffers[10]);              // first word of the workspace
+  // what follows the status block starts at the next 256-byte boundary (the size query allows for the slack):
+  // the partial results are read and written sixteen bytes at a time
   uint8_t* ws = static_cast<uint8_t*>(buffers[10]) + 256;
+  ws += (256 - (reinterpret_cast<uintptr_t>(ws) & 255)) & 255;
   p.tile_prefix = reinterpret_cast<int*>(ws);
   ws += mla::align256((size_t(p.batch) + 1) * sizeof(int));
   p.part_o = reinterpret_cast<float*>(ws);
@@ -563,7 +592,7 @@ extern "C" int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_d
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
   p.workers = sms / (mla::kDimSplit * head_blocks);          // one CTA per SM
   p.workers = p.workers < 1 ? 1 : (p.workers > mla::kMaxWorkers ? mla::kMaxWorkers : p.workers);
-  int rc = int(cudaFuncSetAttribute(mla::mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(mla::kSmemBytes)));
+  int rc = int(cudaFuncSetAttribute(mla::mla_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(mla::kSmemBytes)));
   if (rc) { delete h; return rc; }
   *handle_out = h;
   return 0;
@@ -581,7 +610,8 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
   mla::mla_plan_kernel<<<1, 1024, 0, s>>>(p);
-  mla::mla_decode_kernel<<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
+  if (p.sparse_indices) mla::mla_decode_kernel<true><<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
+  else mla::mla_decode_kernel<false><<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
   {
     // The reduce grid is a programmatic dependent of the decode grid, which takes its launch latency
     // off the end of the operator.
@@ -601,6 +631,96 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
 }
 
 extern "C" int cake_b200_mla_decode_destroy(void* handle) {
+  delete static_cast<cake::mla::Handle*>(handle);
+  return 0;
+}
+
+// ---- sparse form -------------------------------------------------------------------------------
+static bool sparse_mla_config_ok(const cake_b200_sparse_mla_decode_config& c) {
+  return c.num_tokens >= 0 && c.num_tokens <= 65535 && c.num_qo_heads > 0 && c.num_qo_heads <= 65535 * 64 &&
+         c.head_dim_ckv == cake::mla::kCkv && c.head_dim_kpe == cake::mla::kKpe && c.top_k > 0 && c.top_k <= (1 << 20) &&
+         c.num_cache_rows >= 0;
+}
+static cake_b200_mla_decode_config as_dense(const cake_b200_sparse_mla_decode_config& c) {
+  cake_b200_mla_decode_config d{};
+  d.batch = c.num_tokens;
+  d.num_qo_heads = c.num_qo_heads;
+  d.head_dim_ckv = c.head_dim_ckv;
+  d.head_dim_kpe = c.head_dim_kpe;
+  d.page_size = 1;
+  d.max_kv_len = c.top_k;
+  return d;
+}
+
+extern "C" size_t cake_b200_sparse_mla_decode_workspace_bytes(const cake_b200_sparse_mla_decode_config* c) {
+  if (!c || !sparse_mla_config_ok(*c)) return 0;
+  const cake_b200_mla_decode_config d = as_dense(*c);
+  return cake_b200_mla_decode_workspace_bytes(&d) + 256;           // + the sm_scale word the kernel reads
+}
+
+extern "C" int cake_b200_sparse_mla_decode_create(void** buffers, const cake_b200_sparse_mla_decode_config* config, void** handle_out) {
+  using namespace cake;
+  if (!buffers || !config || !handle_out) return kErrBadArgument;
+  *handle_out = nullptr;
+  int device = 0;
+  if (int rc = require_blackwell(&device)) return rc;
+  if (!sparse_mla_config_ok(*config)) return kErrBadArgument;
+  for (int i = 0; i < 7; ++i) {
+    if (!buffers[i] && !(config->num_tokens == 0 && (i == 0 || i == 1 || i == 4 || i == 5))) return kErrBadArgument;
+    if (i <= 3 && (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
+  }
+  if (reinterpret_cast<uintptr_t>(buffers[6]) & 3) return kErrBadArgument;
+  auto* h = new (std::nothrow) mla::Handle;
+  if (!h) return int(cudaErrorMemoryAllocation);
+  h->device = device;
+  mla::Params& p = h->p;
+  p = mla::Params{};
+  p.q_nope = static_cast<const __nv_bfloat16*>(buffers[0]);
+  p.q_pe = static_cast<const __nv_bfloat16*>(buffers[1]);
+  p.ckv = static_cast<const __nv_bfloat16*>(buffers[2]);
+  p.kpe = static_cast<const __nv_bfloat16*>(buffers[3]);
+  p.sparse_indices = static_cast<const int*>(buffers[4]);
+  p.top_k = config->top_k;
+  p.out = static_cast<__nv_bfloat16*>(buffers[5]);
+  p.lse = nullptr;                                         // the contract returns the output only
+  p.batch = int(config->num_tokens);
+  p.heads = config->num_qo_heads;
+  p.page_size = 1;
+  p.status = static_cast<int*>(buffers[6]);                // first word of the workspace
+  // words 16.. of the status block hold the scale, which the contract fixes as a number, not a tensor
+  p.sm_scale = reinterpret_cast<const float*>(p.status + 16);
+  h->sm_scale = config->sm_scale;
+  uint8_t* ws = static_cast<uint8_t*>(buffers[6]) + 256;
+  ws += (256 - (reinterpret_cast<uintptr_t>(ws) & 255)) & 255;
+  p.tile_prefix = reinterpret_cast<int*>(ws);
+  ws += mla::align256((size_t(p.batch) + 1) * sizeof(int));
+  p.part_o = reinterpret_cast<float*>(ws);
+  const cake_b200_mla_decode_config d = as_dense(*config);
+  p.part_lse = p.part_o + mla::slots_for(d) * p.heads * mla::kCkv;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) { delete h; return kErrBadArgument; }
+  const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
+  p.workers = sms / (mla::kDimSplit * head_blocks);
+  p.workers = p.workers < 1 ? 1 : (p.workers > mla::kMaxWorkers ? mla::kMaxWorkers : p.workers);
+  int rc = int(cudaFuncSetAttribute(mla::mla_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(mla::kSmemBytes)));
+  if (rc) { delete h; return rc; }
+  *handle_out = h;
+  return 0;
+}
+
+extern "C" int cake_b200_sparse_mla_decode_launch(void* handle, void* cuda_stream) {
+  using namespace cake;
+  if (!handle) return kErrBadArgument;
+  auto* h = static_cast<mla::Handle*>(handle);
+  if (!h->p.sparse_indices && h->p.batch != 0) return kErrBadArgument;
+  if (h->p.batch == 0) return 0;
+  // the scale travels as a kernel-readable word; the plan kernel clears word 0 of the block only
+  CAKE_CUDA_OK(cudaMemcpyAsync(h->p.status + 16, &h->sm_scale, sizeof(float), cudaMemcpyHostToDevice,
+                               reinterpret_cast<cudaStream_t>(cuda_stream)));
+  return cake_b200_mla_decode_launch(handle, cuda_stream);
+}
+
+extern "C" int cake_b200_sparse_mla_decode_destroy(void* handle) {
   delete static_cast<cake::mla::Handle*>(handle);
   return 0;
 }

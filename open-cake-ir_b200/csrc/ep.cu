@@ -140,7 +140,10 @@ struct Handle {
 }  // namespace cake
 
 static bool ep_config_ok(const cake_b200_ep_config& c) {
-  return c.tokens >= 0 && c.tokens <= (1 << 22) && c.hidden > 0 && c.hidden % 512 == 0 /* packed rows stay 16-byte aligned */ && c.top_k > 0 && c.top_k <= 32 &&
+  // pack and unpack move rows with 16-byte loads and stores, so every row of a send or receive block must start
+  // on a 16-byte boundary: H + 4*H/128 is a multiple of 16 when H % 512 == 0, and 8*top_k when top_k is even
+  return c.tokens >= 0 && c.tokens <= (1 << 22) && c.hidden > 0 && c.hidden % 512 == 0 && c.top_k > 0 && c.top_k <= 32 &&
+         c.top_k % 2 == 0 && cake::ep::row_bytes(c.hidden, c.top_k) % 16 == 0 &&
          c.world > 0 && c.world <= 64 && c.experts > 0 && c.experts % c.world == 0 && c.capacity >= c.tokens;
 }
 

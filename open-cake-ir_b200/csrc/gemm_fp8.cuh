@@ -13,8 +13,7 @@
 // Rows are TMEM lanes (UMMA M = 128), columns are TMEM columns (UMMA N = 256).  For every
 // 128-wide K block, four tcgen05.mma.kind::f8f6f4 (K = 32 each) write a FRESH partial product
 // into one of two TMEM accumulator stages; eight epilogue warps read that stage back
-// (tcgen05.ld), multiply it by the block's scales and add it to fp32 registers ("promotion",
-// packed two-wide fp32 FMAs),
+// (tcgen05.ld), multiply it by the block's scales and add it to fp32 registers ("promotion"),
 // which is what arbitrary fp32 1x128 / 128x128 scales need -- the hardware block-scaled kinds
 // only take power-of-two scales per 32 elements.  While the epilogue promotes block kb the
 // tensor core already works on block kb+1 in the other stage.  Operands arrive through a
@@ -25,12 +24,6 @@
 // hands them to the other roles through a four-slot ring (Params::queue).
 #pragma once
 #include "common.cuh"
-
-// Measurement aid, never set in the shipped build: 1 = the epilogue only hands the accumulator
-// stage back (no tensor-memory reads, results are garbage), 2 = it reads but does not accumulate.
-#ifndef CAKE_GEMM_PROBE
-#define CAKE_GEMM_PROBE 0
-#endif
 
 namespace cake {
 namespace gemm {
@@ -90,6 +83,7 @@ struct Shared {
   uint64_t empty[kStages];
   uint64_t tmem_full[kTmemStages];
   uint64_t tmem_empty[kTmemStages];
+  uint64_t exchange_done;                                   // kGateUp: all epilogue warps have published their amax
   uint64_t item_full[kItemSlots], item_empty[kItemSlots];   // hand-over of drawn work items from the TMA warp to the other roles
   int item_q[kItemSlots];
   uint32_t tmem_base;
@@ -139,6 +133,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
     for (int s = 0; s < kTmemStages; ++s) { mbar_init(&sh->tmem_full[s], 1); mbar_init(&sh->tmem_empty[s], kEpilogueWarps); }
     for (int s = 0; s < kItemSlots; ++s) { mbar_init(&sh->item_full[s], 1); mbar_init(&sh->item_empty[s], 1 + kEpilogueWarps); }
+    mbar_init(&sh->exchange_done, kEpilogueWarps);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -276,6 +271,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int seg_col1 = (MODE == kGateUp) ? 128 + cg * 64 : cg * 128 + 64;
     const int sfb_rows = p.b_rows_per_group / 128;
     uint32_t it = 0, k = 0;
+    uint32_t exchanges = 0;                    // amax exchanges so far (phase of Shared::exchange_done)
     int parity = 0;
     bool ok = true;
     Item item;
@@ -301,9 +297,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       const float* sfb0 = p.sfb + (size_t(item.group) * sfb_rows + sfb_row0) * p.b_k_blocks;
       const float* sfb1 = p.sfb + (size_t(item.group) * sfb_rows + sfb_row1) * p.b_k_blocks;
-      float2 acc[64];                          // 128 fp32 accumulators as pairs for the two-wide FMA
+      float acc[128];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) acc[i] = make_float2(0.f, 0.f);
+      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
       // Scales travel kScaleAhead K blocks ahead of their use: an L2 round trip under a full TMA
       // stream is longer than one K block, and a scale that arrives late stalls the whole promotion.
       constexpr int kScaleAhead = 3;
@@ -320,7 +316,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         sa_q[j] = sb0_q[j] = sb1_q[j] = 0.f;
         if (j < p.k_blocks) fetch(j, sa_q[j], sb0_q[j], sb1_q[j]);
       }
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+      // A warp none of whose 32 rows exists (the tail tile of a group), or whose columns lie past N, only hands
+      // the accumulator stages back: no tensor-memory reads, no arithmetic.
+      const bool warp_active = quad * 32 < item.rows_valid && (MODE == kGateUp || item.n_tile * kBN + cg * 128 < p.n);
+      for (int kb = 0; !warp_active && kb < p.k_blocks; ++kb, ++it) {
+        const int t = it % kTmemStages;
+        ok = mbar_wait(&sh->tmem_full[t], (it / kTmemStages) & 1, abort_flag, p.status, kStatusWaitTmemFull);
+        if (!ok) break;
+        if (lane == 0) mbar_arrive(&sh->tmem_empty[t]);
+      }
+      for (int kb = 0; warp_active && kb < p.k_blocks; ++kb, ++it) {
         const int t = it % kTmemStages;
         const float s0 = sa_q[0] * sb0_q[0], s1 = sa_q[0] * sb1_q[0];
 #pragma unroll
@@ -330,42 +335,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t stage_addr = lane_base + t * kBN;
-#if CAKE_GEMM_PROBE == 1
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->tmem_empty[t]);
-        acc[0].x += s0 + s1;
-        continue;
-#endif
         // two round trips to tensor memory per K block, 64 columns each
         float va[32], vb[32];
         tmem_ld_32x32b_x32(stage_addr + seg_col0, va);
         tmem_ld_32x32b_x32(stage_addr + seg_col0 + 32, vb);
         tcgen05_wait_ld();
-#if CAKE_GEMM_PROBE == 2
-        acc[0].x += va[0] + vb[0] + s0;
-#else
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          acc[i] = ffma2(make_float2(va[2 * i], va[2 * i + 1]), make_float2(s0, s0), acc[i]);
-          acc[16 + i] = ffma2(make_float2(vb[2 * i], vb[2 * i + 1]), make_float2(s0, s0), acc[16 + i]);
+        for (int i = 0; i < 32; ++i) {
+          acc[i] = fmaf(va[i], s0, acc[i]);
+          acc[32 + i] = fmaf(vb[i], s0, acc[32 + i]);
         }
-#endif
         tmem_ld_32x32b_x32(stage_addr + seg_col1, va);
         tmem_ld_32x32b_x32(stage_addr + seg_col1 + 32, vb);
         tcgen05_wait_ld();
         tcgen05_fence_before();            // everything this warp needs has left tensor memory
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->tmem_empty[t]);
-#if CAKE_GEMM_PROBE == 2
-        acc[1].x += va[0] + vb[0] + s1;
-#else
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          acc[32 + i] = ffma2(make_float2(va[2 * i], va[2 * i + 1]), make_float2(s1, s1), acc[32 + i]);
-          acc[48 + i] = ffma2(make_float2(vb[2 * i], vb[2 * i + 1]), make_float2(s1, s1), acc[48 + i]);
+        for (int i = 0; i < 32; ++i) {
+          acc[64 + i] = fmaf(va[i], s1, acc[64 + i]);
+          acc[96 + i] = fmaf(vb[i], s1, acc[96 + i]);
         }
-#endif
       }
       if (!ok) break;
       // rows past the group's end and, where N is an odd multiple of 128, the tile's second column group hold nothing
@@ -375,11 +365,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (valid) {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + cg * 128;
 #pragma unroll
-          for (int i = 0; i < 64; i += 4) {
+          for (int i = 0; i < 128; i += 8) {
             uint4 w;
-            w.x = pack_bf16x2(acc[i].x, acc[i].y); w.y = pack_bf16x2(acc[i + 1].x, acc[i + 1].y);
-            w.z = pack_bf16x2(acc[i + 2].x, acc[i + 2].y); w.w = pack_bf16x2(acc[i + 3].x, acc[i + 3].y);
-            *reinterpret_cast<uint4*>(out + 2 * i) = w;
+            w.x = pack_bf16x2(acc[i], acc[i + 1]); w.y = pack_bf16x2(acc[i + 2], acc[i + 3]);
+            w.z = pack_bf16x2(acc[i + 4], acc[i + 5]); w.w = pack_bf16x2(acc[i + 6], acc[i + 7]);
+            *reinterpret_cast<uint4*>(out + i) = w;
           }
         }
       } else if (MODE == kDown) {
@@ -387,11 +377,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const float w = __ldg(p.row_weight + row);
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + size_t(row) * p.n + item.n_tile * kBN + cg * 128;
 #pragma unroll
-          for (int i = 0; i < 64; i += 4) {
+          for (int i = 0; i < 128; i += 8) {
             uint4 v;
-            v.x = pack_bf16x2(acc[i].x * w, acc[i].y * w); v.y = pack_bf16x2(acc[i + 1].x * w, acc[i + 1].y * w);
-            v.z = pack_bf16x2(acc[i + 2].x * w, acc[i + 2].y * w); v.w = pack_bf16x2(acc[i + 3].x * w, acc[i + 3].y * w);
-            *reinterpret_cast<uint4*>(out + 2 * i) = v;
+            v.x = pack_bf16x2(acc[i] * w, acc[i + 1] * w); v.y = pack_bf16x2(acc[i + 2] * w, acc[i + 3] * w);
+            v.z = pack_bf16x2(acc[i + 4] * w, acc[i + 5] * w); v.w = pack_bf16x2(acc[i + 6] * w, acc[i + 7] * w);
+            *reinterpret_cast<uint4*>(out + i) = v;
           }
         }
       } else {
@@ -399,24 +389,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // group it shares with the thread of the same row in the other column group.
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float g0 = acc[32 + i].x, g1 = acc[32 + i].y;
-          acc[i].x = acc[i].x * (g0 / (1.f + __expf(-g0)));
-          acc[i].y = acc[i].y * (g1 / (1.f + __expf(-g1)));
-          amax = fmaxf(amax, fmaxf(fabsf(acc[i].x), fabsf(acc[i].y)));
+        for (int i = 0; i < 64; ++i) {
+          const float gate = acc[64 + i];
+          acc[i] = acc[i] * (gate / (1.f + __expf(-gate)));
+          amax = fmaxf(amax, fabsf(acc[i]));
         }
         const int out_kb = p.n / 128;                      // K blocks of one term of the output
         const int terms = p.split_act ? 2 : 1;
         uint8_t* out_base = reinterpret_cast<uint8_t*>(p.out) + size_t(row) * (size_t(p.n) * terms) + item.n_tile * 128 + cg * 64;
-        for (int term = 0; term < terms; ++term) {
+        for (int term = 0; term < terms; ++term, ++exchanges) {
+          // The two column groups of a row meet through shared memory.  The hand-over is an mbarrier wait like
+          // every other wait of the kernel: bounded, and given up when another role has raised the abort flag.
           sh->exchange[parity][term][cg][r] = amax;
-          asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->exchange_done);
+          ok = mbar_wait(&sh->exchange_done, exchanges & 1, abort_flag, p.status, kStatusWaitFlag);
+          if (!ok) break;
           const float group_amax = fmaxf(amax, sh->exchange[parity][term][cg ^ 1][r]);
           const float scale = group_amax > 0.f ? group_amax / 448.f : 1.f;
           const float inv = 1.f / scale;
           uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) packed[i >> 1] = pack_e4m3x4(acc[i].x * inv, acc[i].y * inv, acc[i + 1].x * inv, acc[i + 1].y * inv);
+          for (int i = 0; i < 64; i += 4) packed[i >> 2] = pack_e4m3x4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
           if (valid) {
             uint4* dst = reinterpret_cast<uint4*>(out_base + size_t(term) * p.n);
 #pragma unroll
@@ -426,15 +420,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (term + 1 < terms) {        // residual after the first term becomes the value to quantise
             amax = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const uint32_t word = packed[i >> 1];
-              const float r0 = acc[i].x - e4m3_to_float(uint8_t(word >> ((i & 1) * 16))) * scale;
-              const float r1 = acc[i].y - e4m3_to_float(uint8_t(word >> ((i & 1) * 16 + 8))) * scale;
-              acc[i] = make_float2(r0, r1);
-              amax = fmaxf(amax, fmaxf(fabsf(r0), fabsf(r1)));
+            for (int i = 0; i < 64; ++i) {
+              const uint32_t word = packed[i >> 2];
+              acc[i] -= e4m3_to_float(uint8_t(word >> ((i & 3) * 8))) * scale;
+              amax = fmaxf(amax, fabsf(acc[i]));
             }
           }
         }
+        if (!ok) break;
       }
     }
   }

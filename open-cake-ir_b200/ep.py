@@ -1,7 +1,7 @@
 """Expert-parallel FP8 MoE layer: tokens sharded T/R per rank, experts sharded E/R per rank
 (rank r owns experts [r*E/R, (r+1)*E/R), the reference's ``local_expert_offset`` view,
 src/open_cake_ir/tasks/solx_fib/moe.py:139-146), joined by an all-to-all dispatch and an
-all-to-all combine over ``torch.distributed`` (NCCL over NVLink on the GPU box; gloo in the CPU
+all-to-all combine over ``torch.distributed`` (NCCL over NVLink between GPUs; gloo in the CPU
 tests of the exchange logic).
 
 Per layer and rank:
@@ -179,7 +179,7 @@ class NativeExpertParallelMoe:
         cfg = _lib.EpConfig(tokens, cap, hidden, top_k, self.world, experts)
         width = int(_lib.library().cake_b200_ep_row_bytes(ctypes.byref(cfg)))
         if width == 0:
-            raise ValueError("unsupported expert-parallel configuration (hidden must be a multiple of 512)")
+            raise ValueError("unsupported expert-parallel configuration (hidden must be a multiple of 512 and top_k even)")
         i32, f32 = torch.int32, torch.float32
         self.ids = torch.empty((tokens, top_k), dtype=i32, device=dev)
         self.route_weights = torch.empty((tokens, top_k), dtype=f32, device=dev)
@@ -239,22 +239,51 @@ class NativeExpertParallelMoe:
             return self.output
         return self._eager()
 
-    def _eager(self) -> torch.Tensor:
-        with torch.cuda.device(self.device):
-            self.router.launch()
-            self._stage(0)
+    STEP_PARTS = ("route_plan_pack", "dispatch_all_to_all", "unpack", "layer_route_permute_gather", "layer_gemm1_swiglu",
+                  "layer_gemm2", "layer_combine", "return_all_to_all", "reduce")
+
+    def _parts(self):
+        """The parts of one step, in order, as closures on the current stream."""
+        def dispatch():
             if self.world == 1:
                 self.recv.copy_(self.send)
             else:
                 dist.all_to_all_single(self.recv, self.send, group=self.group)
-            self._stage(1)
-            self.layer.launch()
+
+        def give_back():
             if self.world == 1:
                 self.returned.copy_(self.partial.view_as(self.returned))
             else:
                 dist.all_to_all_single(self.returned, self.partial.view_as(self.returned), group=self.group)
-            self._stage(2)
+
+        def route_plan_pack():
+            self.router.launch()
+            self._stage(0)
+
+        return [route_plan_pack, dispatch, lambda: self._stage(1), lambda: self.layer.launch_stage(0),
+                lambda: self.layer.launch_stage(1), lambda: self.layer.launch_stage(2), lambda: self.layer.launch_stage(3),
+                give_back, lambda: self._stage(2)]
+
+    def _eager(self) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            for part in self._parts():
+                part()
         return self.output
+
+    def stage_times(self, steps: int = 5) -> dict:
+        """Mean milliseconds of each part of a step (STEP_PARTS), eager launches with an event after every part.
+        A collective's time includes waiting for the slowest peer to arrive at it."""
+        with torch.cuda.device(self.device):
+            parts = self._parts()
+            events = [[torch.cuda.Event(enable_timing=True) for _ in range(len(parts) + 1)] for _ in range(steps)]
+            for k in range(steps):
+                events[k][0].record()
+                for i, part in enumerate(parts):
+                    part()
+                    events[k][i + 1].record()
+            torch.cuda.synchronize(self.device)
+        return {name: sum(events[k][i].elapsed_time(events[k][i + 1]) for k in range(steps)) / steps
+                for i, name in enumerate(self.STEP_PARTS)}
 
     def close(self):
         if self._handle.value:

@@ -101,6 +101,21 @@ class RmsNorm(_Operator):
         self._create(order, cfg)
 
 
+class AddRmsNorm(_Operator):
+    """``z = bf16(delta + residual); residual_out = z; out = bf16(fp32(z) * rsqrt(mean z^2 + eps) * weight)``
+    (src/open_cake_ir/tasks/add_rmsnorm.py:66): two fresh outputs, the rounded sum is what is normalised."""
+    stem = "add_rmsnorm"
+
+    def __init__(self, delta, residual, weight, out, residual_out, epsilon: float = 1e-6):
+        rows, width = delta.shape
+        _check("delta", delta, "bf16", None); _check("residual", residual, "bf16", (rows, width))
+        _check("weight", weight, "bf16", (width,)); _check("out", out, "bf16", (rows, width))
+        _check("residual_out", residual_out, "bf16", (rows, width))
+        _no_alias({"out": out, "residual_out": residual_out},
+                  {"delta": delta, "residual": residual, "weight": weight, "out": out, "residual_out": residual_out})
+        self._create([delta, residual, weight, out, residual_out], _lib.AddRmsNormConfig(rows, width, float(epsilon)))
+
+
 class BlockScaledGemm(_Operator):
     """``c = bf16((a*sfa) @ (b*sfb)^T)``; a e4m3 [M,K], sfa fp32 [K/128,M], b e4m3 [N,K],
     sfb fp32 [N/128,K/128] (corpus/schedules/block-scaled-gemm-b1-smoke.json)."""
@@ -133,6 +148,34 @@ class MoeRouting(_Operator):
                    "expert_ids": expert_ids, "route_weights": route_weights})
         cfg = _lib.RoutingConfig(tokens, experts, top_k, n_group, topk_group, {"ds": 0, "softmax": 1}[mode])
         self._create([routing_logits, routing_bias, routed_scaling_factor, expert_ids, route_weights], cfg)
+
+
+class V4MoeGate(_Operator):
+    """DeepSeek-V4 gate: sqrt-softplus scores, top-k of score + selection_bias, weights = route_scale *
+    score / sum over the selection (src/open_cake_ir/tasks/deepseek_v4/workload.py:190-201).  Outputs in the
+    contract's order: ``weights`` then ``expert_ids``."""
+    stem = "v4_moe_gate"
+
+    def __init__(self, router_logits, selection_bias, weights, expert_ids, *, top_k=6, route_scale=2.5):
+        tokens, experts = router_logits.shape
+        _check("router_logits", router_logits, "fp32", None); _check("selection_bias", selection_bias, "fp32", (experts,))
+        _check("weights", weights, "fp32", (tokens, top_k)); _check("expert_ids", expert_ids, "int32", (tokens, top_k))
+        _no_alias({"weights": weights, "expert_ids": expert_ids},
+                  {"router_logits": router_logits, "selection_bias": selection_bias, "weights": weights, "expert_ids": expert_ids})
+        self._create([router_logits, selection_bias, weights, expert_ids], _lib.V4GateConfig(tokens, experts, top_k, float(route_scale)))
+
+
+class CsaTopk(_Operator):
+    """DeepSeek-V4 CSA indexer: positions of the ``top_k`` largest of each row's scores, descending
+    (src/open_cake_ir/tasks/deepseek_v4/workload.py:188-189)."""
+    stem = "csa_topk"
+
+    def __init__(self, index_scores, indices):
+        rows, candidates = index_scores.shape
+        top_k = indices.shape[1]
+        _check("index_scores", index_scores, "fp32", None); _check("indices", indices, "int32", (rows, top_k))
+        _no_alias({"indices": indices}, {"index_scores": index_scores, "indices": indices})
+        self._create([index_scores, indices], _lib.TopkConfig(rows, candidates, top_k))
 
 
 class MoePermute(_Operator):
@@ -263,11 +306,38 @@ class MlaPagedDecode(_Operator):
         self._create(tensors, cfg, _lib.workspace_bytes(self.stem, cfg))
 
 
+class SparseMlaDecode(_Operator):
+    """Sparse MLA decode (contracts/workloads/dsa-attention-sparse-mla-decode-v1.json): per query row the cache
+    rows named by the non-negative entries of ``sparse_indices`` (token-level row numbers), softmax over them,
+    output only; ``sm_scale`` is a number of the contract."""
+    stem = "sparse_mla_decode"
+    SM_SCALE = 0.1352337788608801
+
+    def __init__(self, q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, output, *, sm_scale: float = SM_SCALE):
+        tokens, heads, dc = q_nope.shape
+        pages, page_size, _ = ckv_cache.shape
+        dp = q_pe.shape[2]
+        top_k = sparse_indices.shape[1]
+        _check("q_nope", q_nope, "bf16", None); _check("q_pe", q_pe, "bf16", (tokens, heads, dp))
+        _check("ckv_cache", ckv_cache, "bf16", (pages, page_size, dc)); _check("kpe_cache", kpe_cache, "bf16", (pages, page_size, dp))
+        _check("sparse_indices", sparse_indices, "int32", (tokens, top_k)); _check("output", output, "bf16", (tokens, heads, dc))
+        tensors = [q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, output]
+        _no_alias({"output": output}, {str(i): t for i, t in enumerate(tensors)})
+        cfg = _lib.SparseMlaDecodeConfig(tokens, pages * page_size, heads, dc, dp, top_k, float(sm_scale))
+        self._create(tensors, cfg, _lib.workspace_bytes(self.stem, cfg))
+
+
 # ---- functional forms: allocate the outputs, run once on the current stream ------------------
 def rmsnorm(x, weight, epsilon, residual=None):
     out = torch.empty_like(x)
     RmsNorm(x, weight, out, epsilon, residual).launch()
     return out
+
+
+def add_rmsnorm(delta, residual, weight, epsilon: float = 1e-6):
+    out, residual_out = torch.empty_like(delta), torch.empty_like(delta)
+    AddRmsNorm(delta, residual, weight, out, residual_out, epsilon).launch()
+    return out, residual_out
 
 
 def block_scaled_gemm(a, sfa, b, sfb):
@@ -286,6 +356,20 @@ def moe_routing(routing_logits, routing_bias, routed_scaling_factor, *, top_k=8,
     MoeRouting(routing_logits, routing_bias, routed_scaling_factor, ids, weights, top_k=top_k, n_group=n_group,
                topk_group=topk_group, mode=mode).launch()
     return ids, weights
+
+
+def v4_moe_gate(router_logits, selection_bias, *, top_k=6, route_scale=2.5):
+    tokens = router_logits.shape[0]
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=router_logits.device)
+    ids = torch.empty((tokens, top_k), dtype=torch.int32, device=router_logits.device)
+    V4MoeGate(router_logits, selection_bias, weights, ids, top_k=top_k, route_scale=route_scale).launch()
+    return weights, ids
+
+
+def csa_topk(index_scores, top_k=1024):
+    indices = torch.empty((index_scores.shape[0], top_k), dtype=torch.int32, device=index_scores.device)
+    CsaTopk(index_scores, indices).launch()
+    return indices
 
 
 def moe_permute(expert_ids, local_expert_offset, local_experts: int):
@@ -339,3 +423,12 @@ def mla_paged_decode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, 
     MlaPagedDecode(q_nope, q_pe, ckv_cache, kpe_cache, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse,
                    max_kv_len=max_kv_len).launch()
     return output, lse
+
+
+def sparse_mla_decode(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale: float = SparseMlaDecode.SM_SCALE):
+    output = torch.empty_like(q_nope)
+    op = SparseMlaDecode(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, output, sm_scale=sm_scale)
+    op.launch()
+    if op.status():
+        raise RuntimeError("sparse_mla_decode: a device-side wait ran out")
+    return output

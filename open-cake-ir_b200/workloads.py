@@ -133,16 +133,23 @@ def moe_inputs(tokens=4096, hidden=7168, inter=2048, experts=256, local_experts=
     w2 = torch.empty((local_experts, hidden, inter), dtype=torch.float8_e4m3fn, device=device)
     s2 = torch.empty((local_experts, hidden // 128, inter // 128), dtype=torch.float32, device=device)
     for e in range(local_experts):
-        g = _gen(c, 10 + local_offset + e, gen_device, salt)
-        q, s = quantize_blocks_128x128(_randn((2 * inter, hidden), g, gen_device, 0.0, 1.0 / math.sqrt(hidden)))
-        w13[e].copy_(q); s13[e].copy_(s)
-        q, s = quantize_blocks_128x128(_randn((hidden, inter), g, gen_device, 0.0, 1.0 / math.sqrt(inter)))
-        w2[e].copy_(q); s2[e].copy_(s)
+        q13, sc13, q2, sc2 = moe_expert_weights(local_offset + e, hidden, inter, gen_device=gen_device, salt=salt)
+        w13[e].copy_(q13); s13[e].copy_(sc13)
+        w2[e].copy_(q2); s2[e].copy_(sc2)
     inputs = {"routing_logits": logits, "routing_bias": bias, "hidden_states": h, "hidden_states_scale": hs,
               "gemm1_weights": w13, "gemm1_weights_scale": s13, "gemm2_weights": w2, "gemm2_weights_scale": s2,
               "local_expert_offset": torch.tensor([local_offset], dtype=torch.int32),
               "routed_scaling_factor": torch.tensor([2.5], dtype=torch.float32)}
     return {n: t.to(device) for n, t in inputs.items()}
+
+
+def moe_expert_weights(expert: int, hidden=7168, inter=2048, *, gen_device="cpu", salt=0):
+    """The weights of ONE global expert id as ``moe_inputs`` draws them: (w13 e4m3 [2I,H], scales [2I/128,H/128],
+    w2 e4m3 [H,I], scales [H/128,I/128]).  Any rank can regenerate any expert, whoever owns it."""
+    g = _gen("fp8_moe", 10 + expert, gen_device, salt)
+    q13, s13 = quantize_blocks_128x128(_randn((2 * inter, hidden), g, gen_device, 0.0, 1.0 / math.sqrt(hidden)))
+    q2, s2 = quantize_blocks_128x128(_randn((hidden, inter), g, gen_device, 0.0, 1.0 / math.sqrt(inter)))
+    return q13, s13, q2, s2
 
 
 def moe_flops(tokens, hidden, inter, top_k=8) -> int:

@@ -14,4 +14,4 @@ addressing, softmax top-k routing, the canonical permutation order, FP8 requanti
 SwiGLU output) are pinned by reduction to the reference on the cases it does hold plus
 known-answer tests of their own.
 """
-from . import attention, block_scaled_gemm, compare, moe, permute, rmsnorm, routing  # noqa: F401
+from . import add_rmsnorm, attention, block_scaled_gemm, compare, deepseek_v4, moe, permute, rmsnorm, routing  # noqa: F401

@@ -142,3 +142,28 @@ def materialize_reference_case(task: str, variant: str, case_id: str) -> dict[st
             if name in inputs:
                 inputs[name].zero_()
     return inputs
+
+
+def sparse_mla_decode_reference(inputs: dict, sm_scale: float):
+    """Sparse MLA decode as the contract states it (contracts/workloads/dsa-attention-sparse-mla-decode-v1.json,
+    ``semantics.definition``; validator src/open_cake_ir/tasks/dsa/contract.py:5-78): for each query row and head
+    gather the cache rows named by the non-negative token-level ``sparse_indices``, logits =
+    (q_nope . ckv + q_pe . kpe) * sm_scale, softmax over the present entries, times the ckv rows; no present entry
+    gives a row of zeros.  PARITY UNPINNED: the reference holds no executable oracle and no golden vectors for this
+    operator (its baseline is a black box outside the checkout); this restates the definition in fp64, and reduces
+    to ``paged_decode_reference`` (which IS pinned) when the list names a sequence's rows in order."""
+    q_nope, q_pe = inputs["q_nope"], inputs["q_pe"]
+    ckv = inputs["ckv_cache"].reshape(-1, inputs["ckv_cache"].shape[-1]).double()
+    kpe = inputs["kpe_cache"].reshape(-1, inputs["kpe_cache"].shape[-1]).double()
+    tokens, heads, width = q_nope.shape
+    out = torch.zeros((tokens, heads, width), dtype=torch.bfloat16)
+    scale = float(torch.tensor(sm_scale, dtype=torch.float32))      # the fp32 number a device receives
+    for t in range(tokens):
+        idx = inputs["sparse_indices"][t].long()
+        idx = idx[idx >= 0]
+        if idx.numel() == 0:
+            continue
+        keys, positions = ckv[idx], kpe[idx]
+        logits = (keys @ q_nope[t].double().T + positions @ q_pe[t].double().T) * scale        # [L, heads]
+        out[t] = (torch.softmax(logits, 0).T @ keys).to(torch.bfloat16)
+    return out

@@ -13,7 +13,7 @@ if str(ROOT) not in sys.path:
 
 
 def pytest_configure(config):
-    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
+    config.addinivalue_line("markers", "gpu: needs a B200 (select with -m gpu)")
 
 
 def pytest_collection_modifyitems(config, items):

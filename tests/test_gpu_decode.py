@@ -72,7 +72,9 @@ def test_reference_cases(golden, task, variant, case):
                                                     (3, 8, 8, 1, (1, 300)), (7, 16, 8, 5, (0, 133)),
                                                     # KV head counts that take the other range/pair mappings of the kernel
                                                     (3, 8, 1, 16, (1, 900)), (4, 16, 2, 8, (0, 500)), (2, 24, 3, 16, (5, 700)),
-                                                    (3, 64, 16, 16, (1, 600)), (1, 32, 8, 16, (9000, 9000))])
+                                                    (3, 64, 16, 16, (1, 600)), (1, 32, 8, 16, (9000, 9000)),
+                                                    # more than 1024 sequences: the plan kernel's second pass and its carries
+                                                    (1500, 8, 2, 4, (0, 40))])
 def test_gqa_serving_shapes(batch, hq, hkv, page, lens):
     pool = 20000 if batch == 64 else max(400, batch * (lens[1] // page + 2))
     cpu, meta = cake.workloads.gqa_decode_inputs(batch, hq, hkv, 128, page, lens, pool, device="cpu")
@@ -82,7 +84,9 @@ def test_gqa_serving_shapes(batch, hq, hkv, page, lens):
 
 
 @pytest.mark.parametrize("batch,heads,page,lens", [(32, 128, 64, (1024, 8192)), (3, 16, 1, (1, 200)), (4, 128, 64, (0, 700)),
-                                                   (2, 80, 7, (33, 400)), (2, 256, 16, (10, 300)), (1, 128, 64, (20000, 20000))])
+                                                   (2, 80, 7, (33, 400)), (2, 256, 16, (10, 300)), (1, 128, 64, (20000, 20000)),
+                                                   # more than 1024 sequences: the plan kernel's second pass and its carry
+                                                   (1500, 16, 4, (0, 40))])
 def test_mla_serving_shapes(batch, heads, page, lens):
     cpu, meta = cake.workloads.mla_decode_inputs(batch, heads, page, lens, device="cpu")
     want = attention.paged_decode_reference(cpu, mla=True, page_size=page, per_head_loop=False)

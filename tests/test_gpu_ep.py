@@ -1,4 +1,4 @@
-"""GPU test of the expert-parallel layer on two B200s (skipped on a single-GPU box): tokens and
+"""GPU test of the expert-parallel layer on two B200s (skipped where only one is visible): tokens and
 experts sharded over two NCCL ranks with all-to-all dispatch and combine must reproduce the
 single-GPU native layer over all tokens and experts.  Partial rows travel as bf16 and are added in
 fp32, so the comparison is at the bf16 tolerance (rtol 2e-2 / atol 2e-2, Frobenius <= 1e-2)."""
@@ -68,7 +68,7 @@ def test_two_rank_layer_equals_single_gpu_layer(native):
 
 
 def test_single_rank_exchange_is_the_identity():
-    """World size 1 (runs on any GPU box): plan, pack, unpack and reduce around the rank-local layer must
+    """World size 1 (one GPU is enough): plan, pack, unpack and reduce around the rank-local layer must
     reproduce the plain layer bit for bit, since one bf16 partial per token is added to nothing."""
     dev = cake.workloads.moe_inputs(tokens=200, **SHAPE, local_experts=SHAPE["experts"], local_offset=0, routing="softmax",
                                     device="cuda", gen_device="cpu")

@@ -77,3 +77,16 @@ def test_target_document_matches_the_contract_abi():
             assert op["host_abi"][verb] in HEADER, (name, verb)
         assert all(t["mode"] in ("input", "output") for t in op["tensors"])
     assert json.dumps(doc)      # canonical JSON
+
+
+def test_ep_rows_must_stay_sixteen_byte_aligned():
+    """Packed rows are moved with 16-byte loads and stores: configurations whose row width is not a
+    multiple of 16 (odd top_k, hidden not a multiple of 512) are refused by returning 0."""
+    import ctypes
+    lib = cake._lib.library()
+    def width(hidden, top_k):
+        cfg = cake._lib.EpConfig(64, 64, hidden, top_k, 2, 32)
+        return int(lib.cake_b200_ep_row_bytes(ctypes.byref(cfg)))
+    assert width(1024, 8) == 1024 + 32 + 64
+    assert width(1024, 1) == 0 and width(1024, 7) == 0
+    assert width(640, 8) == 0

@@ -136,7 +136,7 @@ def test_softmax_routing_known_answer():
     torch.testing.assert_close(w[1], torch.full((8,), 0.125))
 
 
-@pytest.mark.parametrize("case", ["primary", "mixed_local", "ties"])
+@pytest.mark.parametrize("case", ["primary", "zero_hidden", "all_nonlocal", "mixed_local", "scaled", "ties"])
 def test_moe_oracle_is_bit_identical_to_reference(golden, case):
     inputs = moe_reference_case(case)
     for name, digest in golden.index[f"moe/{case}"]["inputs_sha256"].items():

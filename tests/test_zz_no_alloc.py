@@ -5,16 +5,18 @@ workspace to lend (a server whose pool owns all device memory, a plug-in sandbox
 cannot take an allocation's synchronisation): its split-KV scratch is a fixed array inside the
 library.  The test drives it through the C ABI only, twice in a row on different problems -- the
 second smaller than the first, so stale scratch from the first call would show -- and compares
-each result with the workspace-based entry point on the same inputs at the decode tolerances
-(output atol 2**-16 rtol 2**-7, lse atol 1e-4 rtol 1e-5).  It also checks the refusal above the
-scratch limit."""
+each result with the workspace-based entry point AND with the CPU oracle on the same inputs at the
+decode tolerances (output atol 2**-16 rtol 2**-7, lse atol 1e-4 rtol 1e-5).  It also checks the
+refusal above the scratch limit.  (That the call allocates nothing is a property of its source --
+it names no allocating routine; what torch's allocator counter can show, and the test checks, is
+only that the binding around it made no torch allocation.)"""
 import ctypes
 
 import pytest
 import torch
 
 import open_cake_ir_b200 as cake
-from oracle import compare
+from oracle import attention, compare
 
 pytestmark = pytest.mark.gpu
 
@@ -44,6 +46,11 @@ def one_problem(batch, hq, hkv, page, lens, pool, salt):
     assert ok, f"output: {bad} mismatches, max abs err {err}"
     ok, bad, err = compare.compare(lse, want_lse, atol=1e-4, rtol=1e-5, ieee=True)
     assert ok, f"lse: {bad} mismatches, max abs err {err}"
+    oracle = attention.paged_decode_reference(cpu, mla=False, page_size=page, per_head_loop=False)
+    ok, bad, err = compare.compare(out, oracle["output"], atol=2.0 ** -16, rtol=2.0 ** -7)
+    assert ok, f"output vs oracle: {bad} mismatches, max abs err {err}"
+    ok, bad, err = compare.compare(lse, oracle["lse"], atol=1e-4, rtol=1e-5, ieee=True)
+    assert ok, f"lse vs oracle: {bad} mismatches, max abs err {err}"
 
 
 def test_two_calls_in_a_row_match_the_workspace_entry_point():
