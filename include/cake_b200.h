@@ -58,6 +58,20 @@ int cake_b200_abi_version(void);
  * that gave up (1 smem-full, 2 smem-empty, 3 tmem-full, 4 tmem-empty, 5 flag). */
 int cake_b200_read_status(const void* workspace, void* cuda_stream, int* status_out);
 
+/* Launch facts of a kernel of this library as compiled -- "gemm_fp8_kernel", "gqa_decode_kernel", "mla_decode_kernel":
+ * threads per CTA and dynamic shared-memory bytes (what the reference's consumer reads from a candidate's metadata,
+ * tools/native_cuda_contract.py:150-175; targets/sm_100a_native.json carries the same numbers and is checked against this). */
+int cake_b200_launch_facts(const char* kernel, int* threads_per_cta, int* dynamic_shared_bytes);
+
+/* For tests of the failure path only; never needed by a caller.  Every device-side wait of the tensor-core kernels
+ * (block-scaled GEMM, MoE grouped GEMMs, MLA decode) is bounded; these hooks let a test make one run out
+ * without hanging or faulting anything: `wait_budget_kiloclocks` > 0 shortens the budget of every wait of later
+ * launches to that many x 1024 SM clocks (0 restores the default of about a second), and `skip_load` != 0 makes
+ * a later dense-GEMM launch (its first CTA) or MLA-decode launch (every CTA with three tiles or more) leave one
+ * operand load out, so that the consumer's wait runs out, the kernel unwinds and returns, and the status word is
+ * set.  Process-wide host state. */
+int cake_b200_test_hooks(int wait_budget_kiloclocks, int skip_load);
+
 /* ------------------------------------------------------------------------------------------
  * RMSNorm.  Replaces the emitted RMSNorm starter (src/open_cake_ir/tasks/solx_fib/authoring.py:9-53)
  * for the operator defined at src/open_cake_ir/tasks/solx_fib/workload.py:214-218, :334-358:
@@ -74,11 +88,6 @@ typedef struct {
 int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_config* config, void** handle_out);
 int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream);
 int cake_b200_rmsnorm_destroy(void* handle);
-/* RMSNorm takes no workspace, so its kernels report a bounded wait that ran out (a row's bulk copy that never
- * landed) through a status word inside the library instead: 0, or the code, for the current device since the
- * library was loaded.  Synchronises `cuda_stream`. */
-int cake_b200_rmsnorm_last_status(void* cuda_stream, int* status_out);
-
 /* ------------------------------------------------------------------------------------------
  * Residual add + RMSNorm with two outputs.  Replaces the emitted starter of the reference's
  * `add_rmsnorm_bf16` task (src/open_cake_ir/tasks/add_rmsnorm.py:145-181; definition :66, oracle :131-143):
@@ -86,7 +95,7 @@ int cake_b200_rmsnorm_last_status(void* cuda_stream, int* status_out);
  *   out = bf16( fp32(z) * rsqrt(mean_j fp32(z)^2 + epsilon) * fp32(weight) )
  * The rounded sum is both what is returned as residual_out (compared bit for bit by the contract) and what is
  * normalised.  buffers: delta bf16 [rows,width], residual bf16 [rows,width], weight bf16 [width],
- *          out bf16 [rows,width], residual_out bf16 [rows,width].  width % 8 == 0, width <= 8192.  No workspace.
+ *          out bf16 [rows,width], residual_out bf16 [rows,width].  width % 8 == 0.  No workspace.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   int64_t rows;
@@ -282,6 +291,53 @@ size_t cake_b200_mla_decode_workspace_bytes(const cake_b200_mla_decode_config* c
 int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_decode_config* config, void** handle_out);
 int cake_b200_mla_decode_launch(void* handle, void* cuda_stream);
 int cake_b200_mla_decode_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * Causal prefill, GQA over a paged or a ragged KV store.  Replaces the four-stage attention launch plan
+ * (src/open_cake_ir/tasks/solx_fib/attention.py:190-331) for the prefill branches of the oracle (attention.py:132-183;
+ * specs src/open_cake_ir/tasks/solx_fib/attention_specs.py:85-248): segment b holds query rows
+ * [qo_indptr[b], qo_indptr[b+1]) and KV rows [kv_indptr[b], kv_indptr[b+1]) (pages when paged); query row i of a
+ * segment with q_len and kv_len rows attends to its first min(kv_len, i + 1 + kv_len - q_len) KV rows (attention.py:170);
+ * out bf16, lse base 2.  Empty segments give zeros / -inf; a row of a non-empty segment that sees no KV row gives NaN
+ * when nan_for_masked is set (the reference's ragged and MLA tasks, attention.py:47) and zeros otherwise, lse -inf.
+ * buffers: q bf16 [total_q,Hq,D], k bf16 and v bf16 ([pages,page_size,Hkv,D] paged; [total_kv,Hkv,D] ragged),
+ *          qo_indptr int32 [S+1], kv_indptr int32 [S+1], kv_indices int32 [*] (null when ragged),
+ *          kv_last_page_len int32 [S] (null: every page full; null when ragged), sm_scale fp32 [1],
+ *          output bf16 [total_q,Hq,D], lse fp32 [total_q,Hq], workspace.  D == 128; Hq/Hkv in 1..8; total_q <= 65535.
+ * Every query token is run as a decode sequence of its own over a prefix of its segment's rows.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t total_q;
+  int32_t segments; /* S */
+  int32_t num_qo_heads, num_kv_heads, head_dim, page_size;
+  int32_t ragged;         /* 1: k and v are [total_kv,Hkv,D], kv_indptr counts rows, no kv_indices */
+  int32_t nan_for_masked; /* 1: a fully masked row of a non-empty segment is NaN */
+  int64_t max_kv_len;
+} cake_b200_gqa_prefill_config;
+size_t cake_b200_gqa_prefill_workspace_bytes(const cake_b200_gqa_prefill_config* config);
+int cake_b200_gqa_prefill_create(void** buffers, const cake_b200_gqa_prefill_config* config, void** handle_out);
+int cake_b200_gqa_prefill_launch(void* handle, void* cuda_stream);
+int cake_b200_gqa_prefill_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * Causal prefill, MLA over a paged latent cache (absorbed form); the same rules as above
+ * (spec src/open_cake_ir/tasks/solx_fib/attention_specs.py:293-338, oracle attention.py:164-165, :170-177).
+ * buffers: q_nope bf16 [total_q,H,512], q_pe bf16 [total_q,H,64], ckv_cache bf16 [pages,page_size,512],
+ *          kpe_cache bf16 [pages,page_size,64], qo_indptr int32 [S+1], kv_indptr int32 [S+1], kv_indices int32 [*],
+ *          kv_last_page_len int32 [S] (null: every page full), sm_scale fp32 [1], output bf16 [total_q,H,512],
+ *          lse fp32 [total_q,H], workspace.  total_q <= 65535.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t total_q;
+  int32_t segments;
+  int32_t num_qo_heads, head_dim_ckv, head_dim_kpe, page_size;
+  int32_t nan_for_masked;
+  int64_t max_kv_len;
+} cake_b200_mla_prefill_config;
+size_t cake_b200_mla_prefill_workspace_bytes(const cake_b200_mla_prefill_config* config);
+int cake_b200_mla_prefill_create(void** buffers, const cake_b200_mla_prefill_config* config, void** handle_out);
+int cake_b200_mla_prefill_launch(void* handle, void* cuda_stream);
+int cake_b200_mla_prefill_destroy(void* handle);
 
 /* ------------------------------------------------------------------------------------------
  * Sparse MLA decode (DeepSeek-V3.2 sparse attention).  Implements the operator of the reference's

@@ -8,9 +8,9 @@ native handle (``ops``) and seeded synthetic inputs at serving shapes (``workloa
 There is no CPU fallback: every operator raises if the native library is missing.
 """
 from . import _lib, operators, ops, workloads  # noqa: F401
-from .ops import (AddRmsNorm, BlockScaledGemm, CsaTopk, Fp8Moe, GqaPagedDecode, MlaPagedDecode, MoePermute, MoeRouting, RmsNorm, SparseMlaDecode, V4MoeGate,
-                  add_rmsnorm, block_scaled_gemm, csa_topk, fp8_moe, gqa_paged_decode, mla_paged_decode, moe_permute, moe_routing, rmsnorm, sparse_mla_decode, v4_moe_gate)
+from .ops import (AddRmsNorm, BlockScaledGemm, CsaTopk, GqaCausalPrefill, MlaCausalPrefill, Fp8Moe, GqaPagedDecode, MlaPagedDecode, MoePermute, MoeRouting, RmsNorm, SparseMlaDecode, V4MoeGate,
+                  add_rmsnorm, block_scaled_gemm, csa_topk, gqa_causal_prefill, mla_causal_prefill, fp8_moe, gqa_paged_decode, mla_paged_decode, moe_permute, moe_routing, rmsnorm, sparse_mla_decode, v4_moe_gate)
 
-__all__ = ["AddRmsNorm", "BlockScaledGemm", "CsaTopk", "SparseMlaDecode", "V4MoeGate", "sparse_mla_decode", "csa_topk", "v4_moe_gate", "Fp8Moe", "GqaPagedDecode", "MlaPagedDecode", "MoePermute", "MoeRouting", "RmsNorm",
+__all__ = ["AddRmsNorm", "BlockScaledGemm", "CsaTopk", "GqaCausalPrefill", "MlaCausalPrefill", "gqa_causal_prefill", "mla_causal_prefill", "SparseMlaDecode", "V4MoeGate", "sparse_mla_decode", "csa_topk", "v4_moe_gate", "Fp8Moe", "GqaPagedDecode", "MlaPagedDecode", "MoePermute", "MoeRouting", "RmsNorm",
            "add_rmsnorm", "block_scaled_gemm", "fp8_moe", "gqa_paged_decode", "mla_paged_decode", "moe_permute", "moe_routing",
            "rmsnorm", "operators", "ops", "workloads"]

@@ -79,6 +79,17 @@ class MlaDecodeConfig(Structure):
                 ("page_size", c_int32), ("max_kv_len", c_int64)]
 
 
+class GqaPrefillConfig(Structure):
+    _fields_ = [("total_q", c_int64), ("segments", c_int32), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32),
+                ("head_dim", c_int32), ("page_size", c_int32), ("ragged", c_int32), ("nan_for_masked", c_int32),
+                ("max_kv_len", c_int64)]
+
+
+class MlaPrefillConfig(Structure):
+    _fields_ = [("total_q", c_int64), ("segments", c_int32), ("num_qo_heads", c_int32), ("head_dim_ckv", c_int32),
+                ("head_dim_kpe", c_int32), ("page_size", c_int32), ("nan_for_masked", c_int32), ("max_kv_len", c_int64)]
+
+
 class SparseMlaDecodeConfig(Structure):
     _fields_ = [("num_tokens", c_int64), ("num_cache_rows", c_int64), ("num_qo_heads", c_int32), ("head_dim_ckv", c_int32),
                 ("head_dim_kpe", c_int32), ("top_k", c_int32), ("sm_scale", c_float)]
@@ -97,9 +108,11 @@ OPERATORS = {
     "gqa_decode": (GqaDecodeConfig, True),
     "mla_decode": (MlaDecodeConfig, True),
     "sparse_mla_decode": (SparseMlaDecodeConfig, True),
+    "gqa_prefill": (GqaPrefillConfig, True),
+    "mla_prefill": (MlaPrefillConfig, True),
 }
 # every symbol include/cake_b200.h declares
-EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_rmsnorm_last_status", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
+EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_test_hooks", "cake_b200_launch_facts", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
             "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit",
             "cake_b200_ep_row_bytes", "cake_b200_ep_exchange_create", "cake_b200_ep_exchange_launch_stage",
             "cake_b200_ep_exchange_destroy"]
@@ -119,7 +132,8 @@ def library() -> ctypes.CDLL:
         lib = ctypes.CDLL(str(LIBRARY_PATH))
         lib.cake_b200_abi_version.restype = c_int
         lib.cake_b200_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
-        lib.cake_b200_rmsnorm_last_status.argtypes = [c_void_p, POINTER(c_int)]
+        lib.cake_b200_test_hooks.argtypes = [c_int, c_int]
+        lib.cake_b200_launch_facts.argtypes = [ctypes.c_char_p, POINTER(c_int), POINTER(c_int)]
         lib.cake_b200_moe_intermediate.argtypes = [c_void_p, c_int, POINTER(c_void_p)]
         lib.cake_b200_moe_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
         lib.cake_b200_gqa_decode_noalloc.argtypes = [POINTER(c_void_p), POINTER(GqaDecodeConfig), c_void_p]

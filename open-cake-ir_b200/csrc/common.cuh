@@ -99,6 +99,12 @@ inline int require_blackwell(int* device_out) {
   return 0;
 }
 
+// Threads per CTA and dynamic shared-memory bytes of the main kernel of each tensor-core or decode operator, for the
+// metadata that travels with the library (each defined beside its kernel).
+void gemm_launch_facts(int* threads, int* dynamic_shared_bytes);
+void gqa_decode_launch_facts(int* threads, int* dynamic_shared_bytes);
+void mla_decode_launch_facts(int* threads, int* dynamic_shared_bytes);
+
 inline int sm_count(int device) {
   int n = 148;
   cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
@@ -168,18 +174,39 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // Clock budget of one bounded wait (about one second at B200 clocks).
 constexpr long long kWaitClockBudget = 2000000000LL;
 
+// What a kernel with bounded waits keeps in shared memory for them: the flag any role raises when its wait
+// ran out, and the budget of a wait in units of 1024 clocks (0 = the default above).
+struct WaitControl {
+  int abort_flag;
+  int budget_kiloclocks;
+};
+
+// Test hooks (cake_b200_test_hooks): a short wait budget and a load that a producer leaves out once, so that
+// a test can make a bounded wait run out without hanging or faulting anything.  Host-side state of the
+// library, copied into a kernel's parameters at launch.
+struct TestHooks {
+  int budget_kiloclocks;   // 0 = default budget
+  int skip_load;           // 1 = the first CTA's producer leaves out its second load
+};
+inline TestHooks& test_hooks() {
+  static TestHooks hooks = {0, 0};
+  return hooks;
+}
+
 // Wait for `parity` of `bar`.  Gives up when the budget runs out or when another role of the
-// CTA has already raised `*abort_flag`; on giving up it raises the flag, records `code` in
-// the global status word and returns false so that the caller can unwind.
+// CTA has already raised the abort flag (`abort_flag` points at a WaitControl); on giving up it raises the
+// flag, records `code` in the global status word and returns false so that the caller can unwind.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
+  const int kiloclocks = abort_flag[1];
+  const long long budget = kiloclocks > 0 ? (long long)kiloclocks << 10 : kWaitClockBudget;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - start > kWaitClockBudget) {
+      if (clock64() - start > budget) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -202,13 +229,6 @@ __device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
       " [%0], [%1, {%2, %3}], [%4], %5;"
       ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
-      : "memory");
-}
-// Untiled bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, `bytes` a multiple of 16.
-__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
@@ -364,53 +384,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, float* v) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
-      : "memory");
-}
-
-// One step of a software-pipelined read-out of tensor memory: starts the load of the NEXT 32 fp32 columns
-// (32 lanes x 32 columns at `taddr`) into y, adds x[i] * s to acc[i] for the 32 columns loaded by the step
-// before, then waits for the load.  Load, FMAs and wait are ONE asm statement, so that nothing the compiler
-// schedules or allocates can touch y between tcgen05.ld and tcgen05.wait::ld.
-__device__ __forceinline__ void tmem_ld32_fma32(uint32_t taddr, float (&y)[32], const float (&x)[32], float* acc, float s) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%96];\n\t"
-      "fma.rn.f32 %32, %64, %97, %32;\n\t"
-      "fma.rn.f32 %33, %65, %97, %33;\n\t"
-      "fma.rn.f32 %34, %66, %97, %34;\n\t"
-      "fma.rn.f32 %35, %67, %97, %35;\n\t"
-      "fma.rn.f32 %36, %68, %97, %36;\n\t"
-      "fma.rn.f32 %37, %69, %97, %37;\n\t"
-      "fma.rn.f32 %38, %70, %97, %38;\n\t"
-      "fma.rn.f32 %39, %71, %97, %39;\n\t"
-      "fma.rn.f32 %40, %72, %97, %40;\n\t"
-      "fma.rn.f32 %41, %73, %97, %41;\n\t"
-      "fma.rn.f32 %42, %74, %97, %42;\n\t"
-      "fma.rn.f32 %43, %75, %97, %43;\n\t"
-      "fma.rn.f32 %44, %76, %97, %44;\n\t"
-      "fma.rn.f32 %45, %77, %97, %45;\n\t"
-      "fma.rn.f32 %46, %78, %97, %46;\n\t"
-      "fma.rn.f32 %47, %79, %97, %47;\n\t"
-      "fma.rn.f32 %48, %80, %97, %48;\n\t"
-      "fma.rn.f32 %49, %81, %97, %49;\n\t"
-      "fma.rn.f32 %50, %82, %97, %50;\n\t"
-      "fma.rn.f32 %51, %83, %97, %51;\n\t"
-      "fma.rn.f32 %52, %84, %97, %52;\n\t"
-      "fma.rn.f32 %53, %85, %97, %53;\n\t"
-      "fma.rn.f32 %54, %86, %97, %54;\n\t"
-      "fma.rn.f32 %55, %87, %97, %55;\n\t"
-      "fma.rn.f32 %56, %88, %97, %56;\n\t"
-      "fma.rn.f32 %57, %89, %97, %57;\n\t"
-      "fma.rn.f32 %58, %90, %97, %58;\n\t"
-      "fma.rn.f32 %59, %91, %97, %59;\n\t"
-      "fma.rn.f32 %60, %92, %97, %60;\n\t"
-      "fma.rn.f32 %61, %93, %97, %61;\n\t"
-      "fma.rn.f32 %62, %94, %97, %62;\n\t"
-      "fma.rn.f32 %63, %95, %97, %63;\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
-      : "=&f"(y[0]), "=&f"(y[1]), "=&f"(y[2]), "=&f"(y[3]), "=&f"(y[4]), "=&f"(y[5]), "=&f"(y[6]), "=&f"(y[7]), "=&f"(y[8]), "=&f"(y[9]), "=&f"(y[10]), "=&f"(y[11]), "=&f"(y[12]), "=&f"(y[13]), "=&f"(y[14]), "=&f"(y[15]), "=&f"(y[16]), "=&f"(y[17]), "=&f"(y[18]), "=&f"(y[19]), "=&f"(y[20]), "=&f"(y[21]), "=&f"(y[22]), "=&f"(y[23]), "=&f"(y[24]), "=&f"(y[25]), "=&f"(y[26]), "=&f"(y[27]), "=&f"(y[28]), "=&f"(y[29]), "=&f"(y[30]), "=&f"(y[31]),
-        "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3]), "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7]), "+f"(acc[8]), "+f"(acc[9]), "+f"(acc[10]), "+f"(acc[11]), "+f"(acc[12]), "+f"(acc[13]), "+f"(acc[14]), "+f"(acc[15]), "+f"(acc[16]), "+f"(acc[17]), "+f"(acc[18]), "+f"(acc[19]), "+f"(acc[20]), "+f"(acc[21]), "+f"(acc[22]), "+f"(acc[23]), "+f"(acc[24]), "+f"(acc[25]), "+f"(acc[26]), "+f"(acc[27]), "+f"(acc[28]), "+f"(acc[29]), "+f"(acc[30]), "+f"(acc[31])
-      : "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7]), "f"(x[8]), "f"(x[9]), "f"(x[10]), "f"(x[11]), "f"(x[12]), "f"(x[13]), "f"(x[14]), "f"(x[15]), "f"(x[16]), "f"(x[17]), "f"(x[18]), "f"(x[19]), "f"(x[20]), "f"(x[21]), "f"(x[22]), "f"(x[23]), "f"(x[24]), "f"(x[25]), "f"(x[26]), "f"(x[27]), "f"(x[28]), "f"(x[29]), "f"(x[30]), "f"(x[31]),
-        "r"(taddr), "f"(s)
       : "memory");
 }
 

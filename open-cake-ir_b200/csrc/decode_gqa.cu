@@ -21,6 +21,7 @@
 // shared memory and writes one partial result per piece; the pair that finishes the last piece of
 // a (sequence, KV head) merges the pieces and writes the output, so there is no reduce launch.
 #include "common.cuh"
+#include "prefill.cuh"
 #include "../../include/cake_b200.h"
 #include <mutex>
 #include <new>
@@ -61,9 +62,16 @@ struct Params {
   int* done;                     // [B, Hkv] finished items
   int* status;                   // library status word (may be null)
   int batch, hq, hkv, page_size, capacity, ranges;
+  // Explicit sequence table (causal prefill, where every query token is a sequence of its own over a prefix of its
+  // segment's rows): sequence b holds seq_tokens[b] tokens whose page list starts at kv_indices[seq_start[b]];
+  // null = sequences come from kv_indptr / kv_last_page_len.  With kv_indices null the page list is the
+  // identity (ragged K/V: row r of the cache is token r).
+  const int* seq_start;
+  const int* seq_tokens;
 };
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
+  if (p.seq_tokens) return p.seq_tokens[b];
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
   return pages <= 0 ? 0 : (pages - 1) * p.page_size + p.kv_last_page_len[b];
 }
@@ -108,7 +116,7 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) { return uint32
 __device__ __forceinline__ int lookup_rows(const Params& p, int page_base, int kvh, int tok0, int len, int lane) {
   const int tok = tok0 + (lane & 15);
   if (tok >= len) return -1;
-  const int page = __ldg(p.kv_indices + page_base + tok / p.page_size);
+  const int page = p.kv_indices ? __ldg(p.kv_indices + page_base + tok / p.page_size) : page_base + tok / p.page_size;
   return (page * p.page_size + (tok % p.page_size)) * p.hkv + kvh;   // < 2^31 rows = 512 GiB per cache
 }
 
@@ -157,7 +165,7 @@ gqa_plan_kernel(const Params p) {
     int batch_entries;
     const int first = entries_before + cta1024_exclusive_scan(n, sums32, batch_entries);
     if (b < p.batch) {
-      const int page_base = p.kv_indptr[b];
+      const int page_base = p.seq_start ? p.seq_start[b] : p.kv_indptr[b];
       for (int k = 0; k < n; ++k) {
         const long long range_start = (long long)(first_range + k) * per;
         const long long piece_begin = max(start, range_start), piece_end = min(start + len, range_start + per);
@@ -560,6 +568,8 @@ inline int fill_params(Params& p, void** buffers, const cake_b200_gqa_decode_con
   p.hkv = c.num_kv_heads;
   p.page_size = c.page_size;
   p.status = nullptr;
+  p.seq_start = nullptr;
+  p.seq_tokens = nullptr;
   return 0;
 }
 
@@ -585,6 +595,11 @@ inline int launch(Params& p, int sms, cudaStream_t s) {
 
 }  // namespace gqa
 }  // namespace cake
+
+void cake::gqa_decode_launch_facts(int* threads, int* dynamic_shared_bytes) {
+  *threads = cake::gqa::kWarps * 32;
+  *dynamic_shared_bytes = int(cake::gqa::kSmemBytes);
+}
 
 static bool gqa_config_ok(const cake_b200_gqa_decode_config& c) {
   if (c.batch < 0 || c.batch > 65535 || c.head_dim != cake::gqa::kD || c.page_size <= 0 || c.max_kv_len < 0) return false;
@@ -720,4 +735,113 @@ extern "C" int cake_b200_gqa_decode_noalloc(void** buffers, const cake_b200_gqa_
   if (int rc = gqa::noalloc_setup(device, &scratch)) return rc;
   gqa::carve_scratch(p, static_cast<uint8_t*>(scratch));
   return gqa::launch(p, sms, reinterpret_cast<cudaStream_t>(cuda_stream));
+}
+
+// ------------------------------------------------------------------------------------------
+// Causal prefill (paged or ragged K/V): see prefill.cuh.
+namespace cake {
+namespace gqa {
+struct PrefillHandle {
+  int device, sms;
+  Params p;
+  const int *qo_indptr, *kv_indptr_segments, *last_page_len;
+  int *seq_start, *seq_tokens, *masked;
+  int segments, total_q, kv_unit, nan_for_masked;
+};
+}  // namespace gqa
+}  // namespace cake
+
+static bool gqa_prefill_config_ok(const cake_b200_gqa_prefill_config& c, cake_b200_gqa_decode_config* as_decode) {
+  if (c.total_q < 0 || c.total_q > 65535 || c.segments <= 0 || c.segments > 65535) return false;
+  cake_b200_gqa_decode_config d{};
+  d.batch = c.total_q;
+  d.num_qo_heads = c.num_qo_heads;
+  d.num_kv_heads = c.num_kv_heads;
+  d.head_dim = c.head_dim;
+  d.page_size = c.ragged ? 1 : c.page_size;
+  d.max_kv_len = c.max_kv_len;
+  *as_decode = d;
+  return gqa_config_ok(d);
+}
+
+extern "C" size_t cake_b200_gqa_prefill_workspace_bytes(const cake_b200_gqa_prefill_config* c) {
+  cake_b200_gqa_decode_config d;
+  if (!c || !gqa_prefill_config_ok(*c, &d)) return 0;
+  return cake_b200_gqa_decode_workspace_bytes(&d) + cake::prefill::table_bytes(c->total_q);
+}
+
+extern "C" int cake_b200_gqa_prefill_create(void** buffers, const cake_b200_gqa_prefill_config* config, void** handle_out) {
+  using namespace cake;
+  if (!buffers || !config || !handle_out) return kErrBadArgument;
+  *handle_out = nullptr;
+  int device = 0;
+  if (int rc = require_blackwell(&device)) return rc;
+  cake_b200_gqa_decode_config d;
+  if (!gqa_prefill_config_ok(*config, &d)) return kErrBadArgument;
+  // buffers: q, k, v, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse, workspace;
+  // ragged K/V: kv_indices and kv_last_page_len are null
+  for (int i = 0; i < 11; ++i) {
+    const bool optional = i == 6 || (config->ragged && i == 5);
+    if (!buffers[i] && !optional) return kErrBadArgument;
+    if (i <= 2 && (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
+  }
+  if (config->ragged && (buffers[5] || buffers[6])) return kErrBadArgument;
+  if (reinterpret_cast<uintptr_t>(buffers[10]) & 3) return kErrBadArgument;
+  auto* h = new (std::nothrow) gqa::PrefillHandle;
+  if (!h) return int(cudaErrorMemoryAllocation);
+  h->device = device;
+  gqa::Params& p = h->p;
+  void* as_decode[9] = {buffers[0], buffers[1], buffers[2], buffers[4], buffers[5] ? buffers[5] : buffers[4], buffers[6] ? buffers[6] : buffers[4],
+                        buffers[7], buffers[8], buffers[9]};
+  if (int rc = gqa::fill_params(p, as_decode, d)) { delete h; return rc; }
+  p.kv_indices = static_cast<const int*>(buffers[5]);              // null: identity page list (ragged)
+  p.kv_last_page_len = nullptr;                                    // lengths come from the sequence table
+  p.capacity = int(gqa::entries_for(d, gqa::kMaxSms));
+  p.status = static_cast<int*>(buffers[10]);
+  uint8_t* ws = static_cast<uint8_t*>(buffers[10]) + 256;
+  ws += (256 - (reinterpret_cast<uintptr_t>(ws) & 255)) & 255;
+  const size_t table = prefill::table_bytes(config->total_q) / 3;
+  h->seq_start = reinterpret_cast<int*>(ws);
+  h->seq_tokens = reinterpret_cast<int*>(ws + table);
+  h->masked = reinterpret_cast<int*>(ws + 2 * table);
+  gqa::carve_scratch(p, ws + 3 * table);
+  p.seq_start = h->seq_start;
+  p.seq_tokens = h->seq_tokens;
+  h->qo_indptr = static_cast<const int*>(buffers[3]);
+  h->kv_indptr_segments = static_cast<const int*>(buffers[4]);
+  h->last_page_len = static_cast<const int*>(buffers[6]);
+  h->segments = config->segments;
+  h->total_q = int(config->total_q);
+  h->kv_unit = d.page_size;
+  h->nan_for_masked = config->nan_for_masked;
+  int sms = 0;
+  int rc = gqa_sm_count(device, &sms);
+  if (!rc) rc = int(cudaFuncSetAttribute(gqa::gqa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gqa::kSmemBytes));
+  if (rc) { delete h; return rc; }
+  h->sms = sms < gqa::kMaxSms ? sms : gqa::kMaxSms;
+  *handle_out = h;
+  return 0;
+}
+
+extern "C" int cake_b200_gqa_prefill_launch(void* handle, void* cuda_stream) {
+  using namespace cake;
+  if (!handle) return kErrBadArgument;
+  auto* h = static_cast<gqa::PrefillHandle*>(handle);
+  int device = -1;
+  CAKE_CUDA_OK(cudaGetDevice(&device));
+  if (device != h->device) return kErrWrongDevice;
+  if (h->total_q == 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  prefill::prefill_plan_kernel<<<(h->total_q + 255) / 256, 256, 0, s>>>(h->qo_indptr, h->kv_indptr_segments, h->last_page_len, h->segments,
+                                                                       h->kv_unit, h->total_q, h->seq_start, h->seq_tokens, h->masked);
+  gqa::Params p = h->p;
+  if (int rc = gqa::launch(p, h->sms, s)) return rc;
+  if (h->nan_for_masked)
+    prefill::prefill_mark_kernel<<<(h->total_q + 7) / 8, 256, 0, s>>>(h->masked, h->total_q, p.out, p.hq * gqa::kD);
+  return int(cudaGetLastError());
+}
+
+extern "C" int cake_b200_gqa_prefill_destroy(void* handle) {
+  delete static_cast<cake::gqa::PrefillHandle*>(handle);
+  return 0;
 }

@@ -30,6 +30,7 @@
 // runs.  The running max only moves when it grows by more than 2^8, so O is rescaled in TMEM
 // rarely.  Every wait is bounded and reports through the status word.
 #include "common.cuh"
+#include "prefill.cuh"
 #include "../../include/cake_b200.h"
 #include <new>
 
@@ -79,6 +80,12 @@ struct Params {
   // sparse_indices[b, :] (token-level row numbers page * page_size + offset, -1 = no entry) instead of a page list.
   const int* sparse_indices;
   int top_k;
+  // Explicit sequence table (causal prefill: every query token is a sequence of its own over a prefix of its
+  // segment's rows): sequence b holds seq_tokens[b] tokens whose page list starts at kv_indices[seq_start[b]].
+  const int* seq_start;
+  const int* seq_tokens;
+  int wait_kiloclocks;    // budget of a bounded wait in units of 1024 clocks (0: the default, about a second)
+  int skip_load;          // test hook: a CTA's loader warps leave out the third tile of the first sequence they work on
 };
 
 struct Shared {
@@ -88,7 +95,7 @@ struct Shared {
   uint64_t row_sums;                              // the two softmax warps of a row exchange their sums once
   uint64_t q_moved;                               // Q has left its staging area (ring stages 1..3)
   uint32_t tmem_base;
-  int abort_flag;
+  WaitControl wait;
   float l_part[2][kHeads];
 };
 
@@ -96,6 +103,7 @@ constexpr size_t kSmemBytes = size_t(kQSmemBytes) + size_t(kStages) * kKvStageBy
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
   if (p.sparse_indices) return p.top_k;            // listed entries, some of which may be -1
+  if (p.seq_tokens) return p.seq_tokens[b];
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
   return pages <= 0 ? 0 : (pages - 1) * p.page_size + p.kv_last_page_len[b];
 }
@@ -188,7 +196,7 @@ mla_decode_kernel(const Params p) {
   Shared* sh = reinterpret_cast<Shared*>(base + kQSmemBytes + kStages * kKvStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head0 = hb * kHeads;
-  if (threadIdx.x == 0) sh->abort_flag = 0;
+  if (threadIdx.x == 0) { sh->wait.abort_flag = 0; sh->wait.budget_kiloclocks = p.wait_kiloclocks; }
   if (warp == kMmaWarp) {
     tmem_alloc(&sh->tmem_base, kTmemColumns);
     tmem_relinquish();
@@ -205,6 +213,7 @@ mla_decode_kernel(const Params p) {
   const int upto = min(p.tile_prefix[b + 1], range_end);        // this range holds units [at, upto) of sequence b
   const int first_tile = max(at - p.tile_prefix[b] - kSeqCost, 0);
   const int tiles = upto - p.tile_prefix[b] - kSeqCost - first_tile;
+  const bool first_pass = at == range_begin;      // (test hook below)
   at = upto;
   if (tiles <= 0) continue;                        // only (part of) the sequence's start-up share fell into this range
   const int len = seq_len(p, b);
@@ -240,7 +249,7 @@ mla_decode_kernel(const Params p) {
   cp_async_commit();
   // The first tile goes out while the Q block is in flight (its page lookup is two dependent loads);
   // it is a copy group of its own, so that the barrier below waits for Q only.
-  const int page_base = SPARSE ? b * p.top_k : p.kv_indptr[b];
+  const int page_base = SPARSE ? b * p.top_k : (p.seq_start ? p.seq_start[b] : p.kv_indptr[b]);
   if (warp < kLoaderWarps) load_tile(p, lookup_row(p, page_base, begin, end, threadIdx.x), kv_addr, threadIdx.x);
   cp_async_commit();
   cp_async_wait<1>();
@@ -249,7 +258,7 @@ mla_decode_kernel(const Params p) {
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  volatile int* abort_flag = &sh->abort_flag;
+  volatile int* abort_flag = &sh->wait.abort_flag;
 
   if (warp < kLoaderWarps) {
     // ------------------------------ loader --------------------------------------------
@@ -266,6 +275,7 @@ mla_decode_kernel(const Params p) {
       // stages 1..3 hold the Q block until the softmax warps have moved it to tensor memory
       if (ok && i == 1) ok = mbar_wait(&sh->q_moved, 0, abort_flag, p.status, kStatusWaitFlag);
       if (!ok) break;
+      if (p.skip_load && i == 2 && first_pass) { my_slot = next_slot; continue; }   // test hook: never filled
       load_tile(p, my_slot, kv_addr + s * kKvStageBytes, threadIdx.x);
       cp_async_arrive_on(&sh->kv_full[s]);
       my_slot = next_slot;
@@ -477,7 +487,7 @@ mla_decode_kernel(const Params p) {
   tcgen05_fence_before();
   __syncthreads();                                 // every role is done with this sequence's barriers and tiles
   tcgen05_fence_after();
-  if (sh->abort_flag) break;
+  if (sh->wait.abort_flag) break;
   }
   if (warp == kMmaWarp) tmem_dealloc(sh->tmem_base, kTmemColumns);
 }
@@ -535,6 +545,11 @@ inline size_t slots_for(const cake_b200_mla_decode_config& c) { return size_t(kM
 }  // namespace mla
 }  // namespace cake
 
+void cake::mla_decode_launch_facts(int* threads, int* dynamic_shared_bytes) {
+  *threads = cake::mla::kThreads;
+  *dynamic_shared_bytes = int(cake::mla::kSmemBytes);
+}
+
 static bool mla_config_ok(const cake_b200_mla_decode_config& c) {
   return c.batch >= 0 && c.batch <= 65535 && c.num_qo_heads > 0 && c.num_qo_heads <= 65535 * 64 &&
          c.head_dim_ckv == cake::mla::kCkv && c.head_dim_kpe == cake::mla::kKpe && c.page_size > 0 && c.max_kv_len >= 0;
@@ -577,6 +592,8 @@ extern "C" int cake_b200_mla_decode_create(void** buffers, const cake_b200_mla_d
   p.page_size = config->page_size;
   p.sparse_indices = nullptr;
   p.top_k = 0;
+  p.seq_start = nullptr;
+  p.seq_tokens = nullptr;
   if (reinterpret_cast<uintptr_t>(buffers[10]) & 3) { delete h; return kErrBadArgument; }
   p.status = static_cast<int*>(buffers[10]);              // first word of the workspace
   // what follows the status block starts at the next 256-byte boundary (the size query allows for the slack):
@@ -605,7 +622,9 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   int device = -1;
   CAKE_CUDA_OK(cudaGetDevice(&device));
   if (device != h->device) return kErrWrongDevice;
-  const mla::Params& p = h->p;
+  mla::Params p = h->p;
+  p.wait_kiloclocks = test_hooks().budget_kiloclocks;
+  p.skip_load = test_hooks().skip_load;
   if (p.batch == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
@@ -722,5 +741,100 @@ extern "C" int cake_b200_sparse_mla_decode_launch(void* handle, void* cuda_strea
 
 extern "C" int cake_b200_sparse_mla_decode_destroy(void* handle) {
   delete static_cast<cake::mla::Handle*>(handle);
+  return 0;
+}
+
+// ---- causal prefill (see prefill.cuh) -------------------------------------------------------------
+namespace cake {
+namespace mla {
+struct PrefillHandle {
+  Handle decode;             // first member: the decode launch path takes it as a Handle
+  const int *qo_indptr, *kv_indptr_segments, *last_page_len;
+  int *seq_start, *seq_tokens, *masked;
+  int segments, total_q, kv_unit, nan_for_masked;
+};
+}  // namespace mla
+}  // namespace cake
+
+static bool mla_prefill_config_ok(const cake_b200_mla_prefill_config& c, cake_b200_mla_decode_config* as_decode) {
+  if (c.total_q < 0 || c.total_q > 65535 || c.segments <= 0 || c.segments > 65535) return false;
+  cake_b200_mla_decode_config d{};
+  d.batch = c.total_q;
+  d.num_qo_heads = c.num_qo_heads;
+  d.head_dim_ckv = c.head_dim_ckv;
+  d.head_dim_kpe = c.head_dim_kpe;
+  d.page_size = c.page_size;
+  d.max_kv_len = c.max_kv_len;
+  *as_decode = d;
+  return mla_config_ok(d);
+}
+
+extern "C" size_t cake_b200_mla_prefill_workspace_bytes(const cake_b200_mla_prefill_config* c) {
+  cake_b200_mla_decode_config d;
+  if (!c || !mla_prefill_config_ok(*c, &d)) return 0;
+  return cake_b200_mla_decode_workspace_bytes(&d) + cake::prefill::table_bytes(c->total_q) + 512;      // + this operator's own status block and its alignment slack
+}
+
+extern "C" int cake_b200_mla_prefill_create(void** buffers, const cake_b200_mla_prefill_config* config, void** handle_out) {
+  using namespace cake;
+  if (!buffers || !config || !handle_out) return kErrBadArgument;
+  *handle_out = nullptr;
+  cake_b200_mla_decode_config d;
+  if (!mla_prefill_config_ok(*config, &d)) return kErrBadArgument;
+  // buffers: q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, kv_last_page_len (may be null),
+  //          sm_scale, output, lse, workspace
+  for (int i = 0; i < 12; ++i) if (!buffers[i] && i != 7) return kErrBadArgument;
+  if (reinterpret_cast<uintptr_t>(buffers[11]) & 3) return kErrBadArgument;
+  const size_t tables = prefill::table_bytes(config->total_q);
+  // the decode part of the workspace follows the three per-token tables; its own status block leads it
+  uint8_t* ws = static_cast<uint8_t*>(buffers[11]);
+  uint8_t* table_base = ws + 256;
+  table_base += (256 - (reinterpret_cast<uintptr_t>(table_base) & 255)) & 255;
+  uint8_t* decode_ws = table_base + tables;
+  void* as_decode[11] = {buffers[0], buffers[1], buffers[2], buffers[3], buffers[5], buffers[6], buffers[7] ? buffers[7] : buffers[5],
+                         buffers[8], buffers[9], buffers[10], decode_ws};
+  void* inner = nullptr;
+  if (int rc = cake_b200_mla_decode_create(as_decode, &d, &inner)) return rc;
+  auto* h = new (std::nothrow) mla::PrefillHandle;
+  if (!h) { cake_b200_mla_decode_destroy(inner); return int(cudaErrorMemoryAllocation); }
+  h->decode = *static_cast<mla::Handle*>(inner);
+  cake_b200_mla_decode_destroy(inner);
+  h->decode.p.status = reinterpret_cast<int*>(ws);                // one status word for the operator, at the start
+  h->seq_start = reinterpret_cast<int*>(table_base);
+  h->seq_tokens = reinterpret_cast<int*>(table_base + tables / 3);
+  h->masked = reinterpret_cast<int*>(table_base + 2 * (tables / 3));
+  h->decode.p.seq_start = h->seq_start;
+  h->decode.p.seq_tokens = h->seq_tokens;
+  h->decode.p.kv_last_page_len = nullptr;
+  h->qo_indptr = static_cast<const int*>(buffers[4]);
+  h->kv_indptr_segments = static_cast<const int*>(buffers[5]);
+  h->last_page_len = static_cast<const int*>(buffers[7]);
+  h->segments = config->segments;
+  h->total_q = int(config->total_q);
+  h->kv_unit = config->page_size;
+  h->nan_for_masked = config->nan_for_masked;
+  *handle_out = h;
+  return 0;
+}
+
+extern "C" int cake_b200_mla_prefill_launch(void* handle, void* cuda_stream) {
+  using namespace cake;
+  if (!handle) return kErrBadArgument;
+  auto* h = static_cast<mla::PrefillHandle*>(handle);
+  int device = -1;
+  CAKE_CUDA_OK(cudaGetDevice(&device));
+  if (device != h->decode.device) return kErrWrongDevice;
+  if (h->total_q == 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  prefill::prefill_plan_kernel<<<(h->total_q + 255) / 256, 256, 0, s>>>(h->qo_indptr, h->kv_indptr_segments, h->last_page_len, h->segments,
+                                                                       h->kv_unit, h->total_q, h->seq_start, h->seq_tokens, h->masked);
+  if (int rc = cake_b200_mla_decode_launch(&h->decode, cuda_stream)) return rc;
+  if (h->nan_for_masked)
+    prefill::prefill_mark_kernel<<<(h->total_q + 7) / 8, 256, 0, s>>>(h->masked, h->total_q, h->decode.p.out, h->decode.p.heads * mla::kCkv);
+  return int(cudaGetLastError());
+}
+
+extern "C" int cake_b200_mla_prefill_destroy(void* handle) {
+  delete static_cast<cake::mla::PrefillHandle*>(handle);
   return 0;
 }

@@ -17,6 +17,11 @@ struct DenseHandle {
 }  // namespace
 }  // namespace cake
 
+void cake::gemm_launch_facts(int* threads, int* dynamic_shared_bytes) {
+  *threads = cake::gemm::kThreads;
+  *dynamic_shared_bytes = int(cake::gemm::kSmemBytes);
+}
+
 extern "C" size_t cake_b200_block_scaled_gemm_workspace_bytes(const cake_b200_gemm_config*) { return 256; }
 
 extern "C" int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b200_gemm_config* config,
@@ -70,7 +75,10 @@ extern "C" int cake_b200_block_scaled_gemm_launch(void* handle, void* cuda_strea
   if (device != h->device) return kErrWrongDevice;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
   CAKE_CUDA_OK(cudaMemsetAsync(h->status, 0, 8 * sizeof(int), stream));     // status word and work-item counter
-  gemm::gemm_fp8_kernel<gemm::kDense><<<h->grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(h->map_a, h->map_b, h->params);
+  gemm::Params p = h->params;
+  p.wait_kiloclocks = test_hooks().budget_kiloclocks;
+  p.skip_load = test_hooks().skip_load;
+  gemm::gemm_fp8_kernel<gemm::kDense><<<h->grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(h->map_a, h->map_b, p);
   return int(cudaGetLastError());
 }
 

@@ -76,6 +76,8 @@ struct Params {
   int split_act;               // kGateUp: 1 = also write the residual (lo) term
   int* status;                 // device status word (0 = ok)
   int* queue;                  // device counter, 0 at launch: work items are drawn from it (null: item i goes to CTA i mod grid)
+  int wait_kiloclocks;         // budget of a bounded wait in units of 1024 clocks (0: the default, about a second)
+  int skip_load;               // test hook: CTA 0's producer leaves out the loads of its second K block, once
 };
 
 struct Shared {
@@ -87,7 +89,7 @@ struct Shared {
   uint64_t item_full[kItemSlots], item_empty[kItemSlots];   // hand-over of drawn work items from the TMA warp to the other roles
   int item_q[kItemSlots];
   uint32_t tmem_base;
-  int abort_flag;
+  WaitControl wait;
   int tile_prefix[kMaxGroups + 1];     // m tiles before group g
   float exchange[2][2][2][kBM];        // [item parity][term][column group][row] amax exchange for kGateUp
 };
@@ -134,7 +136,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     for (int s = 0; s < kTmemStages; ++s) { mbar_init(&sh->tmem_full[s], 1); mbar_init(&sh->tmem_empty[s], kEpilogueWarps); }
     for (int s = 0; s < kItemSlots; ++s) { mbar_init(&sh->item_full[s], 1); mbar_init(&sh->item_empty[s], 1 + kEpilogueWarps); }
     mbar_init(&sh->exchange_done, kEpilogueWarps);
-    sh->abort_flag = 0;
+    sh->wait.abort_flag = 0;
+    sh->wait.budget_kiloclocks = p.wait_kiloclocks;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -165,7 +168,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  volatile int* abort_flag = &sh->abort_flag;
+  volatile int* abort_flag = &sh->wait.abort_flag;
 
   if (warp < kControlWarps) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kControlRegs));
@@ -200,6 +203,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int s = it % kStages;
           ok = mbar_wait(&sh->empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
           if (!ok) break;
+          if (p.skip_load && blockIdx.x == 0 && it == 1) continue;      // test hook: this ring slot is never filled
           uint8_t* a_dst = tiles + s * kStageBytes;
           uint8_t* b_dst = a_dst + kBytesA;
           int a_col = kb, b_col = kb;
@@ -435,7 +439,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // ------------------------------ teardown ---------------------------------------------
   tcgen05_fence_before();
   __syncthreads();
-  if (sh->abort_flag) {
+  if (sh->wait.abort_flag) {
     // A wait ran out somewhere: give copies still in flight time to land before the shared
     // memory they target is released with the CTA.
     const long long start = clock64();

@@ -579,14 +579,20 @@ static int moe_launch_stage(cake::moe::MoeHandle* h, int stage, cudaStream_t s) 
           c.top_k, c.local_experts, l.capacity);
       break;
     }
-    case 1:
+    case 1: {
       if (h->p1.queue) CAKE_CUDA_OK(cudaMemsetAsync(h->p1.queue, 0, sizeof(int), s));     // the work-item counter starts at 0
-      gemm::gemm_fp8_kernel<gemm::kGateUp><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a1, h->map_b1, h->p1);
+      gemm::Params p = h->p1;
+      p.wait_kiloclocks = test_hooks().budget_kiloclocks;
+      gemm::gemm_fp8_kernel<gemm::kGateUp><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a1, h->map_b1, p);
       break;
-    case 2:
+    }
+    case 2: {
       if (h->p2.queue) CAKE_CUDA_OK(cudaMemsetAsync(h->p2.queue, 0, sizeof(int), s));
-      gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_b2, h->p2);
+      gemm::Params p = h->p2;
+      p.wait_kiloclocks = test_hooks().budget_kiloclocks;
+      gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_b2, p);
       break;
+    }
     case 3:
       moe::combine_kernel<<<tokens, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(h->ws + l.y), pa.inv_perm, h->output,
                                                  c.hidden, c.top_k);

@@ -1,17 +1,16 @@
-// RMSNorm for sm_100a, fp32 arithmetic, one bf16 rounding of the result.
+// RMSNorm for sm_100a: one CTA per row, the row held in registers between the reduction and the
+// scaling, 128-bit loads and stores, fp32 arithmetic, one bf16 rounding of the result.
 //
 // Operators:
 //   out[r,c] = bf16( z[r,c] * weight[c] / sqrt(mean_j z[r,j]^2 + eps) ),  z = x or fp32(x + residual)
 //     (src/open_cake_ir/tasks/solx_fib/workload.py:214-218, oracle :334-358), and the two-output form
 //   z = bf16(delta + residual); residual_out = z; out = bf16( fp32(z) * rsqrt(mean z^2 + eps) * weight )
-//     (src/open_cake_ir/tasks/add_rmsnorm.py:66, oracle :131-143): the sum is rounded to bf16 FIRST, the
-//     rounded row is what is written back and what is normalised.
-// Both are bound by HBM traffic (2 bytes in and 2 out per element and operand), so what matters is how
-// many bytes an SM keeps in flight.  Rows of up to 16 KiB go through `rmsnorm_ring_kernel`: small
-// persistent CTAs whose rows arrive by untiled bulk copies (cp.async.bulk, one elected thread) in a ring
-// of shared-memory slots, several rows ahead of the one being reduced, so that the loads in flight do
-// not depend on registers or on the row's reduction.  Wider rows use `rmsnorm_kernel`, which holds the row
-// in registers (one CTA per row, next row prefetched).
+//     (src/open_cake_ir/tasks/add_rmsnorm.py:66, oracle :131-143): the sum is rounded to bf16 FIRST, and the
+//     rounded row is both what is written back and what is normalised.
+// The kernel is bound by HBM traffic: 2 bytes in and 2 out per element and operand, plus the weight row.
+// (A variant that staged rows in shared memory through a ring of bulk copies, several rows ahead, was built
+// and measured: 18.4 to 25.5 us on 4096 x 4096 against 15.9 us for this kernel and 14.3 us for a plain copy of
+// the same bytes -- a row's wait -> reduce -> write chain per CTA costs more than the deeper prefetch gains.)
 #include "common.cuh"
 #include "../../include/cake_b200.h"
 #include <new>
@@ -54,11 +53,13 @@ __device__ __forceinline__ float sum_squares8(const uint4& raw) {
 // the weights stay in registers as the packed bf16 they arrived as (4 registers per vector) and
 // are unpacked where they are used; with one vector per thread the kernel fits 40 registers, so an
 // SM holds 1536 threads, each with the next row's vector already in flight (48 KiB of loads per SM).
-template <int kThreads, int VPT, bool RESIDUAL>
+// MODE: 0 = x only; 1 = z = fp32(x + residual); 2 = z = bf16(x + residual), also written to residual_out.
+template <int kThreads, int VPT, int MODE>
 __global__ void __launch_bounds__(kThreads, VPT == 1 ? 1536 / kThreads : ((2048 / kThreads) / VPT > 0 ? (2048 / kThreads) / VPT : 1))
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
-               int rows, int width, float eps) {
+               __nv_bfloat16* __restrict__ residual_out, int rows, int width, float eps) {
+  constexpr bool RESIDUAL = MODE != 0;
   __shared__ float partial[2][kThreads / 32];
   const int vectors = width >> 3;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -104,10 +105,16 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
         unpack8(idx < vectors ? ld_stream(reinterpret_cast<const uint4*>(residual + size_t(row) * width) + idx)
                               : make_uint4(0, 0, 0, 0), r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          z[RESIDUAL ? i : 0][j] += r[j];
-          ss = fmaf(z[RESIDUAL ? i : 0][j], z[RESIDUAL ? i : 0][j], ss);
+        for (int j = 0; j < 8; ++j) z[RESIDUAL ? i : 0][j] += r[j];
+        if (MODE == 2) {                     // the rounding seam: the bf16 sum is returned and normalised
+          float* zz = z[RESIDUAL ? i : 0];
+          uint4 q;
+          q.x = pack_bf16x2(zz[0], zz[1]); q.y = pack_bf16x2(zz[2], zz[3]); q.z = pack_bf16x2(zz[4], zz[5]); q.w = pack_bf16x2(zz[6], zz[7]);
+          unpack8(q, zz);
+          if (idx < vectors) st_stream(reinterpret_cast<uint4*>(residual_out + size_t(row) * width) + idx, q);
         }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(z[RESIDUAL ? i : 0][j], z[RESIDUAL ? i : 0][j], ss);
       }
     } else {
 #pragma unroll
@@ -144,188 +151,33 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
   }
 }
 
-// ---- bulk-copy ring ------------------------------------------------------------------------
-constexpr int kRingThreads = 128;
-constexpr int kRingMaxSlots = 8;
-enum RingMode : int { kPlain = 0, kFusedResidual = 1, kAddTwoOutputs = 2 };
-
-// Set when a wait for a row's bulk copy ran out (never in correct operation); read by
-// cake_b200_rmsnorm_last_status.
-__device__ int g_rmsnorm_status = 0;
-
-struct RingParams {
-  const __nv_bfloat16 *x, *residual, *weight;
-  __nv_bfloat16 *out, *residual_out;
-  int rows, width, slots;
-  float eps;
-};
-
-// Dynamic shared memory: weight row | slots x (x row [| residual row]) ; static: barriers, partial sums.
-template <int MODE>
-__global__ void __launch_bounds__(kRingThreads)
-rmsnorm_ring_kernel(const RingParams p) {
-  extern __shared__ __align__(128) uint8_t ring_smem[];
-  __shared__ uint64_t full[kRingMaxSlots];
-  __shared__ float partial[2][kRingThreads / 32];
-  __shared__ int give_up;
-  constexpr int kOperands = MODE == kPlain ? 1 : 2;
-  const int vectors = p.width >> 3;
-  const uint32_t row_bytes = uint32_t(p.width) * 2u;
-  const uint32_t slot_bytes = row_bytes * kOperands;
-  uint8_t* w_smem = ring_smem;
-  uint8_t* slots = ring_smem + row_bytes;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int my_rows = p.rows > int(blockIdx.x) ? (p.rows - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.slots; ++s) mbar_init(&full[s], 1);
-    give_up = 0;
-    fence_barrier_init();
-  }
-  for (int i = threadIdx.x; i < vectors; i += kRingThreads)
-    reinterpret_cast<uint4*>(w_smem)[i] = __ldg(reinterpret_cast<const uint4*>(p.weight) + i);
-  __syncthreads();
-  const uint64_t once = l2_policy_evict_first();
-  auto request = [&](int k) {            // the CTA's k-th row -> slot k mod slots (one thread)
-    const int s = k % p.slots;
-    const size_t row = size_t(blockIdx.x) + size_t(k) * gridDim.x;
-    uint8_t* dst = slots + size_t(s) * slot_bytes;
-    mbar_arrive_expect_tx(&full[s], slot_bytes);
-    bulk_load_1d(dst, p.x + row * p.width, row_bytes, &full[s], once);
-    if (kOperands == 2) bulk_load_1d(dst + row_bytes, p.residual + row * p.width, row_bytes, &full[s], once);
-  };
-  if (threadIdx.x == 0)
-    for (int k = 0; k < p.slots && k < my_rows; ++k) request(k);
-  const float inv_width = 1.f / float(p.width);
-  for (int k = 0; k < my_rows; ++k) {
-    const int s = k % p.slots;
-    const uint32_t phase = uint32_t(k / p.slots) & 1u;
-    if (!mbar_try_wait(&full[s], phase)) {           // bounded: about a second, then the CTA gives the launch up
-      const long long start = clock64();
-      while (!mbar_try_wait(&full[s], phase)) {
-        if (clock64() - start > kWaitClockBudget) { give_up = 1; atomicCAS(&g_rmsnorm_status, 0, kStatusWaitSmemFull); break; }
-      }
-    }
-    __syncthreads();
-    if (give_up) break;
-    const size_t row = size_t(blockIdx.x) + size_t(k) * gridDim.x;
-    const uint4* xs = reinterpret_cast<const uint4*>(slots + size_t(s) * slot_bytes);
-    const uint4* rs = reinterpret_cast<const uint4*>(slots + size_t(s) * slot_bytes + row_bytes);
-    // z of one 16-byte vector, as the operator defines it
-    auto load_z = [&](int idx, float* z, uint4* rounded) {
-      unpack8(xs[idx], z);
-      if (MODE != kPlain) {
-        float r[8];
-        unpack8(rs[idx], r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) z[j] += r[j];
-      }
-      if (MODE == kAddTwoOutputs) {                  // the rounding seam: z = bf16(delta + residual)
-        uint4 q;
-        q.x = pack_bf16x2(z[0], z[1]); q.y = pack_bf16x2(z[2], z[3]); q.z = pack_bf16x2(z[4], z[5]); q.w = pack_bf16x2(z[6], z[7]);
-        unpack8(q, z);
-        *rounded = q;
-      }
-    };
-    float ss = 0.f;
-    for (int idx = threadIdx.x; idx < vectors; idx += kRingThreads) {
-      float z[8];
-      uint4 q;
-      load_z(idx, z, &q);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(z[j], z[j], ss);
-    }
-    ss = warp_sum(ss);
-    if (lane == 0) partial[k & 1][warp] = ss;
-    __syncthreads();
-    float total = 0.f;
-#pragma unroll
-    for (int i = 0; i < kRingThreads / 32; ++i) total += partial[k & 1][i];
-    const float inverse = 1.f / sqrtf(total * inv_width + p.eps);
-    uint4* dst = reinterpret_cast<uint4*>(p.out + row * p.width);
-    for (int idx = threadIdx.x; idx < vectors; idx += kRingThreads) {
-      float z[8], wf[8];
-      uint4 q;
-      load_z(idx, z, &q);
-      unpack8(reinterpret_cast<const uint4*>(w_smem)[idx], wf);
-      uint4 o;
-      o.x = pack_bf16x2(z[0] * inverse * wf[0], z[1] * inverse * wf[1]);
-      o.y = pack_bf16x2(z[2] * inverse * wf[2], z[3] * inverse * wf[3]);
-      o.z = pack_bf16x2(z[4] * inverse * wf[4], z[5] * inverse * wf[5]);
-      o.w = pack_bf16x2(z[6] * inverse * wf[6], z[7] * inverse * wf[7]);
-      st_stream(dst + idx, o);
-      if (MODE == kAddTwoOutputs) st_stream(reinterpret_cast<uint4*>(p.residual_out + row * p.width) + idx, q);
-    }
-    __syncthreads();                                 // every thread has read the slot for the last time
-    if (threadIdx.x == 0 && k + p.slots < my_rows) {
-      fence_proxy_async_smem();                      // generic-proxy reads of the slot before the async-proxy refill
-      request(k + p.slots);
-    }
-  }
-  if (give_up) {                                     // copies may still be in flight into this CTA's shared memory
-    const long long start = clock64();
-    while (clock64() - start < 2000000LL) __nanosleep(1000);
-  }
-}
-
-// Resident CTAs per SM and ring depth for `rows` rows of `row_bytes` x `operands`: the CTA count per SM
-// (2..6) that leaves the least idle time in the last round of rows, with at least two slots each.
-inline bool ring_plan(int rows, uint32_t row_bytes, int operands, int sms, int* grid, int* slots, size_t* smem) {
-  const size_t budget = 216 * 1024;
-  int best_c = 0, best_slots = 0;
-  double best_eff = 0.0;
-  for (int c = 6; c >= 2; --c) {
-    const size_t per_cta = budget / c;
-    if (per_cta < row_bytes + 2 * size_t(row_bytes) * operands) continue;
-    int sl = int((per_cta - row_bytes) / (size_t(row_bytes) * operands));
-    sl = sl > kRingMaxSlots ? kRingMaxSlots : sl;
-    const int ctas = sms * c;
-    const int rounds = (rows + ctas - 1) / ctas;
-    const double eff = rows >= ctas ? double(rows) / (double(rounds) * ctas) : 1.0;
-    if (eff > best_eff + 1e-9) { best_eff = eff; best_c = c; best_slots = sl; }
-  }
-  if (!best_c) return false;
-  const int ctas = sms * best_c;
-  *grid = rows < ctas ? (rows < 1 ? 1 : rows) : ctas;
-  *slots = best_slots;
-  *smem = row_bytes + size_t(best_slots) * row_bytes * operands;
-  return true;
-}
-
 struct Handle {
   int device;
   const __nv_bfloat16 *x, *residual, *weight;
-  __nv_bfloat16* out;
+  __nv_bfloat16 *out, *residual_out;
   int rows, width;
   float eps;
   int vpt;
   int grid;
-  bool ring;                 // rows go through the bulk-copy ring
-  int ring_mode, ring_grid, ring_slots;
-  size_t ring_smem;
-  __nv_bfloat16* residual_out;
 };
 
-template <int MODE>
-int launch_ring(const Handle* h, cudaStream_t stream) {
-  RingParams p{h->x, h->residual, h->weight, h->out, h->residual_out, h->rows, h->width, h->ring_slots, h->eps};
-  rmsnorm_ring_kernel<MODE><<<h->ring_grid, kRingThreads, h->ring_smem, stream>>>(p);
-  return int(cudaGetLastError());
-}
-
-template <int MODE>
-int prepare_ring(Handle* h, int device, int operands) {
-  h->ring = ring_plan(h->rows, uint32_t(h->width) * 2u, operands, sm_count(device), &h->ring_grid, &h->ring_slots, &h->ring_smem);
-  h->ring_mode = MODE;
-  if (!h->ring) return 0;
-  return int(cudaFuncSetAttribute(rmsnorm_ring_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(h->ring_smem)));
+inline void choose_shape(Handle* h, int device) {
+  const int vectors = h->width / 8;
+  // shape class: 0 = 256 threads x 1 vector; 1..4 = 512 threads x 1, 2, 4, 8 vectors
+  h->vpt = vectors <= 256 ? 0 : vectors <= 512 ? 1 : vectors <= 1024 ? 2 : vectors <= 2048 ? 3 : 4;
+  // persistent CTAs: as many as are resident at once, each walking rows with a stride of the grid
+  const int resident = sm_count(device) * (h->vpt == 0 ? 6 : h->vpt == 1 ? 3 : h->vpt == 2 ? 2 : 1);
+  h->grid = h->rows < 1 ? 1 : (h->rows < resident ? h->rows : resident);
 }
 
 template <int kThreads, int VPT>
 void launch(const Handle* h, cudaStream_t stream) {
-  if (h->residual)
-    rmsnorm_kernel<kThreads, VPT, true><<<h->grid, kThreads, 0, stream>>>(h->x, h->residual, h->weight, h->out, h->rows, h->width, h->eps);
+  if (h->residual_out)
+    rmsnorm_kernel<kThreads, VPT, 2><<<h->grid, kThreads, 0, stream>>>(h->x, h->residual, h->weight, h->out, h->residual_out, h->rows, h->width, h->eps);
+  else if (h->residual)
+    rmsnorm_kernel<kThreads, VPT, 1><<<h->grid, kThreads, 0, stream>>>(h->x, h->residual, h->weight, h->out, nullptr, h->rows, h->width, h->eps);
   else
-    rmsnorm_kernel<kThreads, VPT, false><<<h->grid, kThreads, 0, stream>>>(h->x, nullptr, h->weight, h->out, h->rows, h->width, h->eps);
+    rmsnorm_kernel<kThreads, VPT, 0><<<h->grid, kThreads, 0, stream>>>(h->x, nullptr, h->weight, h->out, nullptr, h->rows, h->width, h->eps);
 }
 
 }  // namespace
@@ -353,27 +205,16 @@ extern "C" int cake_b200_rmsnorm_create(void** buffers, const cake_b200_rmsnorm_
   h->residual = config->fused_residual ? static_cast<const __nv_bfloat16*>(buffers[i++]) : nullptr;
   h->weight = static_cast<const __nv_bfloat16*>(buffers[i++]);
   h->out = static_cast<__nv_bfloat16*>(buffers[i++]);
+  h->residual_out = nullptr;
   h->rows = int(config->rows);
   h->width = int(config->width);
   h->eps = config->epsilon;
-  const int vectors = h->width / 8;
-  // shape class: 0 = 256 threads x 1 vector; 1..4 = 512 threads x 1, 2, 4, 8 vectors
-  h->vpt = vectors <= 256 ? 0 : vectors <= 512 ? 1 : vectors <= 1024 ? 2 : vectors <= 2048 ? 3 : 4;
-  // persistent CTAs: as many as are resident at once, each walking rows with a stride of the grid
-  const int resident = sm_count(device) * (h->vpt == 0 ? 6 : h->vpt == 1 ? 3 : h->vpt == 2 ? 2 : 1);
-  h->grid = h->rows < 1 ? 1 : (h->rows < resident ? h->rows : resident);
-  h->residual_out = nullptr;
-  // rows of up to 16 KiB go through the bulk-copy ring; wider rows stay with the register kernel
-  h->ring = false;
-  if (h->width <= 8192) {
-    const int rc = h->residual ? prepare_ring<kFusedResidual>(h, device, 2) : prepare_ring<kPlain>(h, device, 1);
-    if (rc) { delete h; return rc; }
-  }
+  choose_shape(h, device);
   *handle_out = h;
   return 0;
 }
 
-extern "C" int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream) {
+static int rmsnorm_launch_any(void* handle, void* cuda_stream) {
   using namespace cake;
   if (!handle) return kErrBadArgument;
   auto* h = static_cast<Handle*>(handle);
@@ -382,7 +223,6 @@ extern "C" int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream) {
   if (device != h->device) return kErrWrongDevice;
   if (h->rows == 0) return 0;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
-  if (h->ring) return h->residual ? launch_ring<kFusedResidual>(h, stream) : launch_ring<kPlain>(h, stream);
   switch (h->vpt) {
     case 0: launch<256, 1>(h, stream); break;
     case 1: launch<512, 1>(h, stream); break;
@@ -392,6 +232,8 @@ extern "C" int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream) {
   }
   return int(cudaGetLastError());
 }
+
+extern "C" int cake_b200_rmsnorm_launch(void* handle, void* cuda_stream) { return rmsnorm_launch_any(handle, cuda_stream); }
 
 extern "C" int cake_b200_rmsnorm_destroy(void* handle) {
   delete static_cast<cake::Handle*>(handle);
@@ -409,14 +251,12 @@ extern "C" int cake_b200_add_rmsnorm_create(void** buffers, const cake_b200_add_
     const bool may_be_empty = config->rows == 0 && i != 2;              // only the weight row exists then
     if ((!buffers[i] && !may_be_empty) || (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
   }
-  // the reference bounds a row at 16384 columns (src/open_cake_ir/tasks/add_rmsnorm.py:44); the ring holds two
-  // operand rows per slot, which fits up to 8192 columns
-  if (config->rows < 0 || config->rows > INT32_MAX || config->width <= 0 || (config->width & 7) || config->width > 8192 ||
-      !(config->epsilon >= 0.f))
+  // the reference bounds a row at 16384 columns (src/open_cake_ir/tasks/add_rmsnorm.py:44)
+  if (config->rows < 0 || config->rows > INT32_MAX || config->width <= 0 || (config->width & 7) ||
+      config->width > 8 * 8 * kMaxThreads || !(config->epsilon >= 0.f))
     return kErrBadArgument;
   auto* h = new (std::nothrow) Handle;
   if (!h) return int(cudaErrorMemoryAllocation);
-  *h = Handle{};
   h->device = device;
   h->x = static_cast<const __nv_bfloat16*>(buffers[0]);               // delta
   h->residual = static_cast<const __nv_bfloat16*>(buffers[1]);
@@ -426,35 +266,14 @@ extern "C" int cake_b200_add_rmsnorm_create(void** buffers, const cake_b200_add_
   h->rows = int(config->rows);
   h->width = int(config->width);
   h->eps = config->epsilon;
-  const int rc = prepare_ring<kAddTwoOutputs>(h, device, 2);
-  if (rc || !h->ring) { delete h; return rc ? rc : kErrBadArgument; }
+  choose_shape(h, device);
   *handle_out = h;
   return 0;
 }
 
-extern "C" int cake_b200_add_rmsnorm_launch(void* handle, void* cuda_stream) {
-  using namespace cake;
-  if (!handle) return kErrBadArgument;
-  auto* h = static_cast<Handle*>(handle);
-  int device = -1;
-  CAKE_CUDA_OK(cudaGetDevice(&device));
-  if (device != h->device) return kErrWrongDevice;
-  if (h->rows == 0) return 0;
-  return launch_ring<kAddTwoOutputs>(h, reinterpret_cast<cudaStream_t>(cuda_stream));
-}
+extern "C" int cake_b200_add_rmsnorm_launch(void* handle, void* cuda_stream) { return rmsnorm_launch_any(handle, cuda_stream); }
 
 extern "C" int cake_b200_add_rmsnorm_destroy(void* handle) {
   delete static_cast<cake::Handle*>(handle);
-  return 0;
-}
-
-// 0, or the code of a bulk-copy wait that ran out in any RMSNorm launch on the current device since the
-// library was loaded (synchronises `cuda_stream`).
-extern "C" int cake_b200_rmsnorm_last_status(void* cuda_stream, int* status_out) {
-  using namespace cake;
-  if (!status_out) return kErrBadArgument;
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
-  CAKE_CUDA_OK(cudaMemcpyFromSymbolAsync(status_out, g_rmsnorm_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
-  CAKE_CUDA_OK(cudaStreamSynchronize(s));
   return 0;
 }

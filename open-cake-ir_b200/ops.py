@@ -66,6 +66,21 @@ class _Operator:
                 pointers.append(base)
             self.native = _lib.NativeHandle(self.stem, pointers, config)
 
+    def _create_with_optional(self, tensors: list, config, workspace_bytes: int):
+        """As ``_create`` for an ABI with optional buffers: ``None`` entries are passed as null pointers."""
+        present = [t for t in tensors if t is not None]
+        devices = {t.device for t in present}
+        if len(devices) != 1:
+            raise ValueError("all tensors must be on one device")
+        self.device = devices.pop()
+        self._keep = present
+        pointers = [0 if t is None else t.data_ptr() for t in tensors]
+        with torch.cuda.device(self.device):
+            self.workspace = torch.empty(workspace_bytes + 256, dtype=torch.uint8, device=self.device)
+            self.workspace_ptr = (self.workspace.data_ptr() + 255) // 256 * 256
+            pointers.append(self.workspace_ptr)
+            self.native = _lib.NativeHandle(self.stem, pointers, config)
+
     def launch(self, stream=None) -> None:
         with torch.cuda.device(self.device):
             self.native.launch(_stream(stream))
@@ -327,6 +342,64 @@ class SparseMlaDecode(_Operator):
         self._create(tensors, cfg, _lib.workspace_bytes(self.stem, cfg))
 
 
+class GqaCausalPrefill(_Operator):
+    """Causal GQA prefill over a paged (``kv_indices`` given) or ragged (``kv_indices`` None; ``k``/``v`` are
+    ``[total_kv, Hkv, D]``) KV store; tensors as in attention_specs.py:85-248 plus the optional ``kv_last_page_len``.
+    ``nan_for_masked``: a row of a non-empty segment that sees no KV row is NaN (the reference's ragged tasks) instead of zero."""
+    stem = "gqa_prefill"
+
+    def __init__(self, q, k, v, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse, *, max_kv_len: int,
+                 nan_for_masked: bool | None = None):
+        total_q, hq, d = q.shape
+        ragged = kv_indices is None
+        segments = qo_indptr.shape[0] - 1
+        if ragged:
+            total_kv, hkv, _ = k.shape
+            page_size = 1
+            _check("k", k, "bf16", (total_kv, hkv, d)); _check("v", v, "bf16", (total_kv, hkv, d))
+        else:
+            pages, page_size, hkv, _ = k.shape
+            _check("k_cache", k, "bf16", (pages, page_size, hkv, d)); _check("v_cache", v, "bf16", (pages, page_size, hkv, d))
+            _check("kv_indices", kv_indices, "int32", None)
+        _check("q", q, "bf16", None); _check("qo_indptr", qo_indptr, "int32", (segments + 1,))
+        _check("kv_indptr", kv_indptr, "int32", (segments + 1,)); _check("sm_scale", sm_scale, "fp32", (1,))
+        _check("output", output, "bf16", (total_q, hq, d)); _check("lse", lse, "fp32", (total_q, hq))
+        if kv_last_page_len is not None:
+            _check("kv_last_page_len", kv_last_page_len, "int32", (segments,))
+        present = [t for t in (q, k, v, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse) if t is not None]
+        _no_alias({"output": output, "lse": lse}, {str(i): t for i, t in enumerate(present)})
+        nan = ragged if nan_for_masked is None else bool(nan_for_masked)
+        cfg = _lib.GqaPrefillConfig(total_q, segments, hq, hkv, d, page_size, int(ragged), int(nan), int(max_kv_len))
+        self._create_with_optional([q, k, v, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse], cfg,
+                                   _lib.workspace_bytes(self.stem, cfg))
+
+
+class MlaCausalPrefill(_Operator):
+    """Causal MLA prefill over a paged latent cache; tensors as in attention_specs.py:293-338 plus the optional
+    ``kv_last_page_len``.  A row of a non-empty segment that sees no KV row is NaN (attention.py:47)."""
+    stem = "mla_prefill"
+
+    def __init__(self, q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output,
+                 lse, *, max_kv_len: int, nan_for_masked: bool = True):
+        total_q, heads, dc = q_nope.shape
+        pages, page_size, _ = ckv_cache.shape
+        dp = q_pe.shape[2]
+        segments = qo_indptr.shape[0] - 1
+        _check("q_nope", q_nope, "bf16", None); _check("q_pe", q_pe, "bf16", (total_q, heads, dp))
+        _check("ckv_cache", ckv_cache, "bf16", (pages, page_size, dc)); _check("kpe_cache", kpe_cache, "bf16", (pages, page_size, dp))
+        _check("qo_indptr", qo_indptr, "int32", (segments + 1,)); _check("kv_indptr", kv_indptr, "int32", (segments + 1,))
+        _check("kv_indices", kv_indices, "int32", None); _check("sm_scale", sm_scale, "fp32", (1,))
+        _check("output", output, "bf16", (total_q, heads, dc)); _check("lse", lse, "fp32", (total_q, heads))
+        if kv_last_page_len is not None:
+            _check("kv_last_page_len", kv_last_page_len, "int32", (segments,))
+        present = [t for t in (q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale,
+                               output, lse) if t is not None]
+        _no_alias({"output": output, "lse": lse}, {str(i): t for i, t in enumerate(present)})
+        cfg = _lib.MlaPrefillConfig(total_q, segments, heads, dc, dp, page_size, int(nan_for_masked), int(max_kv_len))
+        self._create_with_optional([q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, kv_last_page_len,
+                                    sm_scale, output, lse], cfg, _lib.workspace_bytes(self.stem, cfg))
+
+
 # ---- functional forms: allocate the outputs, run once on the current stream ------------------
 def rmsnorm(x, weight, epsilon, residual=None):
     out = torch.empty_like(x)
@@ -432,3 +505,26 @@ def sparse_mla_decode(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_sca
     if op.status():
         raise RuntimeError("sparse_mla_decode: a device-side wait ran out")
     return output
+
+
+def gqa_causal_prefill(q, k, v, qo_indptr, kv_indptr, sm_scale, kv_indices=None, kv_last_page_len=None, max_kv_len=None,
+                       nan_for_masked=None):
+    page_size = 1 if kv_indices is None else k.shape[1]
+    if max_kv_len is None:
+        max_kv_len = int((kv_indptr[1:] - kv_indptr[:-1]).max().item()) * page_size
+    output = torch.empty_like(q)
+    lse = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
+    GqaCausalPrefill(q, k, v, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse, max_kv_len=max_kv_len,
+                     nan_for_masked=nan_for_masked).launch()
+    return output, lse
+
+
+def mla_causal_prefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, sm_scale, kv_last_page_len=None,
+                       max_kv_len=None, nan_for_masked=True):
+    if max_kv_len is None:
+        max_kv_len = int((kv_indptr[1:] - kv_indptr[:-1]).max().item()) * ckv_cache.shape[1]
+    output = torch.empty_like(q_nope)
+    lse = torch.empty(q_nope.shape[:2], dtype=torch.float32, device=q_nope.device)
+    MlaCausalPrefill(q_nope, q_pe, ckv_cache, kpe_cache, qo_indptr, kv_indptr, kv_indices, kv_last_page_len, sm_scale, output, lse,
+                     max_kv_len=max_kv_len, nan_for_masked=nan_for_masked).launch()
+    return output, lse

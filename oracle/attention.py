@@ -167,3 +167,131 @@ def sparse_mla_decode_reference(inputs: dict, sm_scale: float):
         logits = (keys @ q_nope[t].double().T + positions @ q_pe[t].double().T) * scale        # [L, heads]
         out[t] = (torch.softmax(logits, 0).T @ keys).to(torch.bfloat16)
     return out
+
+
+# --- causal prefill --------------------------------------------------------------------------
+PREFILL_TASKS = {
+    # task: (mla, paged, heads, kv_heads, captured axes, captured scale)   attention_specs.py:85-248, :293-338
+    "gqa_paged_prefill_kv4": (False, True, 32, 4, dict(len_indptr=2, total_q=1, num_kv_indices=33, num_pages=50), 0.08838834764831843),
+    "gqa_paged_prefill_kv8": (False, True, 32, 8, dict(len_indptr=2, total_q=34, num_kv_indices=1, num_pages=2), 0.08838834764831843),
+    "gqa_ragged_prefill_kv4": (False, False, 32, 4, dict(len_indptr=2, total_q=6, total_kv=6), 0.0883883461356163),
+    "gqa_ragged_prefill_kv8": (False, False, 32, 8, dict(len_indptr=2, total_q=7, total_kv=7), 0.0883883461356163),
+    "mla_paged_prefill_h16": (True, True, 16, 1, dict(len_indptr=2, total_q=33, num_kv_indices=34, num_pages=989669), 0.1352337747812271),
+}
+
+
+def prefill_nan_rule(task: str) -> bool:
+    """A fully masked row of a non-empty segment is NaN for the MLA and the ragged tasks, zero for paged GQA
+    (attention.py:47: ``nan_masked = not decode and (mla or not paged)``)."""
+    mla, paged = PREFILL_TASKS[task][:2]
+    return mla or not paged
+
+
+def causal_prefill_reference(inputs: dict, *, mla: bool, paged: bool, page_size: int = 1, nan_for_masked: bool,
+                             per_head_loop: bool = True):
+    """The prefill branches of attention.py:132-183, with the page size and the last page's fill generalised
+    exactly as for decode.  Segment b: query rows [qo_indptr[b], qo_indptr[b+1]), KV rows of its pages (paged) or
+    rows [kv_indptr[b], kv_indptr[b+1]) of ``k``/``v`` (ragged); query row qi sees its first
+    ``min(kv_len, qi - qs + 1 + kv_len - q_len)`` KV rows (:170); a row that sees none is NaN or zero by the task's
+    rule with lse -inf (:171-173); segments without query or KV rows are skipped (:160-162)."""
+    q = inputs["q_nope"] if mla else inputs["q"]
+    count, heads, _ = q.shape
+    qptr, kvptr = inputs["qo_indptr"].tolist(), inputs["kv_indptr"].tolist()
+    last = inputs.get("kv_last_page_len")
+    width = inputs["ckv_cache"].shape[-1] if mla else q.shape[2]
+    result = torch.zeros((count, heads, width), dtype=torch.bfloat16)
+    lse = torch.full((count, heads), -float("inf"), dtype=torch.float32)
+    scale = float(inputs["sm_scale"][0])
+    for b in range(len(kvptr) - 1):
+        qs, qe = qptr[b:b + 2]
+        ks, ke = kvptr[b:b + 2]
+        if qs == qe or ks == ke:
+            continue
+        if paged:
+            full_last = torch.full((len(kvptr) - 1,), page_size, dtype=torch.int32) if last is None else last
+            args = (inputs["kv_indptr"], inputs["kv_indices"], full_last, b, page_size)
+            if mla:
+                keys = _gather_rows(inputs["ckv_cache"], *args).double()
+                positions = _gather_rows(inputs["kpe_cache"], *args).double()
+                values = keys
+            else:
+                keys = _gather_rows(inputs["k_cache"], *args).double()
+                values = _gather_rows(inputs["v_cache"], *args).double()
+        else:
+            keys, values = inputs["k"][ks:ke].double(), inputs["v"][ks:ke].double()
+        kv_len = keys.shape[0]
+        if kv_len == 0:
+            continue
+        for qi in range(qs, qe):
+            valid = min(kv_len, qi - qs + 1 + kv_len - (qe - qs))
+            if valid <= 0:
+                if nan_for_masked:
+                    result[qi].fill_(float("nan"))
+                continue
+            if per_head_loop:
+                for h in range(heads):
+                    if mla:
+                        logits = (keys[:valid] @ inputs["q_nope"][qi, h].double() + positions[:valid] @ inputs["q_pe"][qi, h].double()) * scale
+                        vals = values[:valid]
+                    else:
+                        kh = h // (heads // keys.shape[1])
+                        logits = (keys[:valid, kh] @ q[qi, h].double()) * scale
+                        vals = values[:valid, kh]
+                    lse[qi, h] = torch.logsumexp(logits, 0) / math.log(2)
+                    result[qi, h] = (torch.softmax(logits, 0) @ vals).to(torch.bfloat16)
+            else:
+                if mla:
+                    logits = (keys[:valid] @ inputs["q_nope"][qi].double().T + positions[:valid] @ inputs["q_pe"][qi].double().T) * scale
+                    out = torch.softmax(logits, 0).T @ values[:valid]
+                else:
+                    kv_heads = keys.shape[1]
+                    qb = q[qi].double().reshape(kv_heads, heads // kv_heads, -1)
+                    logits = torch.einsum("lkd,kgd->lkg", keys[:valid], qb) * scale
+                    out = torch.einsum("lkg,lkd->kgd", torch.softmax(logits, 0), values[:valid]).reshape(heads, -1)
+                    logits = logits.reshape(valid, heads)
+                lse[qi] = (torch.logsumexp(logits, 0) / math.log(2)).float()
+                result[qi] = out.to(torch.bfloat16)
+    return {"output": result, "lse": lse}
+
+
+def materialize_prefill_case(task: str, variant: str, case_id: str) -> dict[str, torch.Tensor]:
+    """Inputs of one reference prefill case (attention.py:101-129): as for decode, plus ``qo_indptr`` splitting the
+    query rows evenly over the segments; the boundary variant has two segments, six query rows and five KV
+    entries (attention.py:16-28)."""
+    mla, paged, heads, kv_heads, axes, scale = PREFILL_TASKS[task]
+    if variant == "captured":
+        axes = dict(axes)
+    else:
+        axes = dict(len_indptr=3, total_q=6)
+        axes.update(dict(num_pages=11, num_kv_indices=5) if paged else dict(total_kv=5))
+    batch = axes["len_indptr"] - 1
+    qcount = axes["total_q"]
+    kvcount = axes["num_kv_indices"] if paged else axes["total_kv"]
+    g = torch.Generator(device="cpu").manual_seed(2801 + CASES.index(case_id))
+    if mla:
+        shapes = {"q_nope": (qcount, heads, 512), "q_pe": (qcount, heads, 64),
+                  "ckv_cache": (axes["num_pages"], 1, 512), "kpe_cache": (axes["num_pages"], 1, 64)}
+    elif paged:
+        shapes = {"q": (qcount, heads, 128), "k_cache": (axes["num_pages"], 1, kv_heads, 128), "v_cache": (axes["num_pages"], 1, kv_heads, 128)}
+    else:
+        shapes = {"q": (qcount, heads, 128), "k": (kvcount, kv_heads, 128), "v": (kvcount, kv_heads, 128)}
+    inputs = {}
+    for name, shape in shapes.items():
+        inputs[name] = (torch.rand(shape, generator=g, dtype=torch.float32) - 0.5).to(torch.bfloat16)
+    qptr = [i * qcount // batch for i in range(batch + 1)]
+    kptr = [i * kvcount // batch for i in range(batch + 1)]
+    if case_id == "segmented" and batch > 1:
+        kptr[1] = 0
+    inputs["kv_indptr"] = torch.tensor(kptr, dtype=torch.int32)
+    inputs["qo_indptr"] = torch.tensor(qptr, dtype=torch.int32)
+    if paged:
+        ids = (torch.arange(kvcount, dtype=torch.int64) * 3 + 1) % axes["num_pages"]
+        if case_id == "permuted":
+            ids = ids.flip(0)
+        inputs["kv_indices"] = ids.to(torch.int32)
+    inputs["sm_scale"] = torch.tensor([scale * (1.75 if case_id == "scaled" else 1.0)], dtype=torch.float32)
+    if case_id == "zeros":
+        for name in ("q", "q_nope", "q_pe"):
+            if name in inputs:
+                inputs[name].zero_()
+    return inputs

@@ -3,7 +3,8 @@
 ``python tests/golden/make_golden_next.py <path-to-reference>`` imports, from ``<reference>/src``, the
 two-output add + RMSNorm task (``open_cake_ir.tasks.add_rmsnorm``, five cases at R=128, C=2560) and the
 two DeepSeek-V4 routing tasks (``open_cake_ir.tasks.deepseek_v4.workload``: MoE gate and CSA indexer
-top-k, four cases each at four rows), materialises every case with the reference's materialiser, runs
+top-k, four cases each at four rows) and the five causal-prefill attention tasks
+(``open_cake_ir.tasks.solx_fib.attention``: captured and boundary variants, five cases each), materialises every case with the reference's materialiser, runs
 the reference's oracle and stores the oracle OUTPUTS (or, where the reference's oracle refuses its own
 case because scores tie after rounding, the refusal) plus a SHA-256 of every INPUT tensor in
 ``next_outputs.npz`` / ``next_index.json``.  The test-suite regenerates the inputs with the restated
@@ -63,6 +64,27 @@ def main(reference: str) -> None:
                 else:
                     arrays[f"{key}/{name}"] = raw(torch.tensor(values, dtype=torch.float64).float())
             print(key, flush=True)
+
+    # Causal prefill: GQA paged kv4 / kv8, GQA ragged kv4 / kv8 and MLA paged, captured + boundary, five cases each.
+    from open_cake_ir.tasks import workloads as registry
+    from open_cake_ir.tasks.solx_fib import attention
+    contracts = Path(reference) / "contracts" / "workloads"
+    for task, stem in (("gqa_paged_prefill_kv4", "solx-fib-gqa-paged-prefill-causal-h32-kv4-d128-ps1-bf16-b300-{v}-v1"),
+                       ("gqa_paged_prefill_kv8", "solx-fib-gqa-paged-prefill-causal-h32-kv8-d128-ps1-bf16-b300-{v}-v1"),
+                       ("gqa_ragged_prefill_kv4", "solx-fib-gqa-ragged-prefill-causal-h32-kv4-d128-bf16-b300-{v}-v1"),
+                       ("gqa_ragged_prefill_kv8", "solx-fib-gqa-ragged-prefill-causal-h32-kv8-d128-bf16-b300-{v}-v1"),
+                       ("mla_paged_prefill_h16", "solx-fib-mla-paged-prefill-causal-h16-ckv512-kpe64-ps1-bf16-b300-{v}-v1")):
+        for variant in ("captured", "boundary"):
+            w = registry.load_workload(contracts / (stem.format(v=variant) + ".json"))
+            for case in w.case_ids:
+                inputs = attention.materialize_tensors(w, case)
+                ref = attention.reference_tensors(w, case, inputs)
+                key = f"prefill/{task}/{variant}/{case}"
+                index[key] = {"inputs_sha256": {n: sha(t) for n, t in inputs.items()}, "output_shape": list(ref["output"].shape),
+                              "nan_for_masked": w.document["semantics"]["fully_masked_nonempty_segment_output"] == "nan"}
+                arrays[key + "/output"] = raw(ref["output"])
+                arrays[key + "/lse"] = raw(ref["lse"])
+                print(key, flush=True)
 
     np.savez_compressed(HERE / "next_outputs.npz", **arrays)
     (HERE / "next_index.json").write_text(json.dumps(index, indent=1, sort_keys=True) + "\n")

@@ -46,7 +46,7 @@ def test_add_rmsnorm_reference_cases(case):
     assert ok, f"{bad} mismatches, max abs err {err}"
 
 
-@pytest.mark.parametrize("rows,width", [(4096, 4096), (1, 8), (3, 2048 + 8), (7, 8192), (0, 256)])
+@pytest.mark.parametrize("rows,width", [(4096, 4096), (1, 8), (3, 2048 + 8), (7, 8192), (5, 16384), (0, 256)])
 def test_add_rmsnorm_serving_and_edge_shapes(rows, width):
     g = torch.Generator().manual_seed(rows * 31 + width)
     cpu = {"delta": torch.randn((rows, width), generator=g).to(torch.bfloat16),
@@ -62,18 +62,6 @@ def test_add_rmsnorm_serving_and_edge_shapes(rows, width):
     assert torch.equal(res.cpu().view(torch.int16), whole.view(torch.int16))
     ok, bad, err = compare.compare(out[sample], want["out"], atol=2.0 ** -16, rtol=1 / 64)
     assert ok, f"{bad} mismatches, max abs err {err}"
-
-
-def test_add_rmsnorm_rejects_rows_wider_than_the_ring():
-    x = torch.zeros((2, 16384), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(cake._lib.CakeError):
-        cake.AddRmsNorm(x, x.clone(), torch.zeros(16384, dtype=torch.bfloat16, device="cuda"), torch.empty_like(x), torch.empty_like(x))
-
-
-def test_rmsnorm_status_word_is_clear():
-    import ctypes
-    out = ctypes.c_int(-1)
-    assert cake._lib.library().cake_b200_rmsnorm_last_status(None, ctypes.byref(out)) == 0 and out.value == 0
 
 
 # ---- DeepSeek-V4 gate and indexer -----------------------------------------------------------

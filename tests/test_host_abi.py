@@ -79,6 +79,31 @@ def test_target_document_matches_the_contract_abi():
     assert json.dumps(doc)      # canonical JSON
 
 
+def test_target_document_carries_the_launch_metadata_of_the_build():
+    """What the reference's consumer validates in a candidate's metadata (tools/native_cuda_contract.py:150-175):
+    arguments / argument_order / signature in ABI order, block == [threads_per_cta, 1, 1], dynamic shared bytes, the
+    exact architecture selectors and the link libraries -- checked against the build script and the compiled constants."""
+    import ctypes
+    import importlib.util
+    doc = cake.operators.target()
+    spec = importlib.util.spec_from_file_location("cake_b200_build", ROOT / "open-cake-ir_b200" / "build.py")
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)
+    selectors = [f for f in build.NVCC_FLAGS if any(k in f for k in ("gpu-architecture", "gpu-code", "-arch", "gencode"))]
+    assert selectors == doc["nvcc_flags"] == ["--gpu-architecture=compute_100a", "--gpu-code=sm_100a"]
+    assert [f for f in build.NVCC_FLAGS if f not in selectors and f not in ("-Xptxas", "-v")] == doc["nvcc_other_flags"]
+    assert doc["link_libraries"] == ["cudart_static"]
+    lib = cake._lib.library()
+    for name, op in doc["operators"].items():
+        assert op["arguments"] == op["tensors"] and op["argument_order"] == [t["name"] for t in op["tensors"]]
+        assert op["signature"] == {t["name"]: "*" + t["dtype"] for t in op["tensors"]}
+        kernel = op["main_kernel"]
+        assert kernel["block"] == [kernel["threads_per_cta"], 1, 1] and kernel["dynamic_shared_bytes"] >= 0
+        threads, smem = ctypes.c_int(), ctypes.c_int()
+        if lib.cake_b200_launch_facts(kernel["name"].encode(), ctypes.byref(threads), ctypes.byref(smem)) == 0:
+            assert (kernel["threads_per_cta"], kernel["dynamic_shared_bytes"]) == (threads.value, smem.value), name
+
+
 def test_ep_rows_must_stay_sixteen_byte_aligned():
     """Packed rows are moved with 16-byte loads and stores: configurations whose row width is not a
     multiple of 16 (odd top_k, hidden not a multiple of 512) are refused by returning 0."""
