@@ -348,7 +348,7 @@ def gather_rows(local: torch.Tensor, world: int, rank: int):
     return torch.cat([p.cpu() for p in parts]) if rank == 0 else None
 
 
-def ep_parity(world, rank, layer, dev):
+def ep_parity(world, rank, layer, dev, layer_class):
     """The expert-parallel path against the CPU oracle, before anything is timed (the oracle is the checker
     here and nothing else).  (a) A small layer (512 tokens, hidden 1024, intermediate 512, 32 experts) through the
     same exchange on all ranks, gathered and compared with the oracle over the WHOLE problem.  (b) At the bench
@@ -362,8 +362,8 @@ def ep_parity(world, rank, layer, dev):
     t_local, e_local = tokens // world, small["experts"] // world
     sd = cake.workloads.moe_inputs(tokens=t_local, **small, local_experts=e_local, local_offset=rank * e_local, routing="softmax",
                                    device="cuda", gen_device="cpu", first_token=rank * t_local, total_tokens=tokens)
-    small_layer = ep.NativeExpertParallelMoe(sd, sd["routing_logits"], sd["routing_bias"], sd["hidden_states"],
-                                             sd["hidden_states_scale"], experts=small["experts"], routing="softmax")
+    small_layer = layer_class(sd, sd["routing_logits"], sd["routing_bias"], sd["hidden_states"],
+                              sd["hidden_states_scale"], experts=small["experts"], routing="softmax")
     for _ in range(2):                       # twice: every buffer is reused between steps
         got_local = small_layer.forward()
     torch.cuda.synchronize()
@@ -406,7 +406,7 @@ def ep_parity(world, rank, layer, dev):
     return record
 
 
-def moe_parallel(steps, warmup, world, rank, cohorts):
+def moe_parallel(steps, warmup, world, rank, cohorts, exchange):
     import torch.distributed as dist
 
     import open_cake_ir_b200 as cake
@@ -415,10 +415,10 @@ def moe_parallel(steps, warmup, world, rank, cohorts):
     dev = cake.workloads.moe_inputs(tokens=t_local, hidden=SHAPE["hidden"], inter=SHAPE["inter"], experts=SHAPE["experts"],
                                     local_experts=e_local, local_offset=rank * e_local, routing="softmax", device="cuda",
                                     gen_device="cuda", first_token=rank * t_local, total_tokens=SHAPE["tokens"])
-    layer = ep.NativeExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
-                                       dev["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"],
-                                       routing="softmax")
-    parity = ep_parity(world, rank, layer, dev)
+    layer_class = ep.PushExpertParallelMoe if exchange == "push" else ep.NativeExpertParallelMoe
+    layer = layer_class(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                        dev["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"], routing="softmax")
+    parity = ep_parity(world, rank, layer, dev, layer_class)
     verdict = torch.tensor([1 if (rank != 0 or parity.get("ok")) else 0], device="cuda")
     dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
     if int(verdict.item()) == 0:
@@ -439,13 +439,15 @@ def moe_parallel(steps, warmup, world, rank, cohorts):
     clocks = ClockSampler(torch.cuda.current_device())
     clocks.__enter__()
     samples = [time_steps(step, steps, warmup if c == 0 else 1, world) for c in range(cohorts)]
+    if exchange == "push" and layer.status():
+        raise RuntimeError("a wait for another rank's rows ran out")
+
     def make_set():
         inputs = dict(dev)
         for k in E2E_INPUTS:
             inputs[k] = torch.empty_like(dev[k])
-        twin = ep.NativeExpertParallelMoe(inputs, inputs["routing_logits"], inputs["routing_bias"], inputs["hidden_states"],
-                                          inputs["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"],
-                                          routing="softmax")
+        twin = layer_class(inputs, inputs["routing_logits"], inputs["routing_bias"], inputs["hidden_states"],
+                           inputs["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"], routing="softmax")
 
         twin.forward()
         if graph:
@@ -462,7 +464,8 @@ def moe_parallel(steps, warmup, world, rank, cohorts):
     flops = cake.workloads.moe_flops(SHAPE["tokens"], SHAPE["hidden"], SHAPE["inter"])
     return {"ms": statistics.median(samples), "cohorts": cohort_stats(samples), "flops": flops, "clocks": clocks.summary(),
             "e2e_ms": e2e_ms, "h2d": h2d * world, "d2h": d2h * world, "launches": layer.launches_per_step * steps,
-            "rows_sent_rank0": int((layer.slot_of >= 0).sum().item()), "ep_parity": parity, "stage_ms": stage_ms,
+            "rows_sent_rank0": layer.rows_sent() if exchange == "push" else int((layer.slot_of >= 0).sum().item()),
+            "ep_parity": parity, "stage_ms": stage_ms, "exchange": exchange,
             "step_mode": "one CUDA graph per step" if graph else "eager launches"}
 
 
@@ -693,6 +696,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--cohorts", type=int, default=3, help="repetitions of the timed region of --steps steps")
     parser.add_argument("--impl", default="native", choices=["native", "reference"])
+    parser.add_argument("--exchange", default="push", choices=["push", "nccl"],
+                        help="expert-parallel exchange: ranks write into each other's memory (push) or NCCL all-to-all")
     parser.add_argument("--skip-operators", action="store_true", help="time only the MoE layer")
     parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baselines")
     parser.add_argument("--profile-case", default=None, choices=["moe", "gemm", "rmsnorm", "gqa", "mla"],
@@ -719,7 +724,7 @@ def main():
     if world == 1:
         r = moe_single(args.steps, warmup, peaks, cohorts)
     else:
-        r = moe_parallel(args.steps, warmup, world, rank, cohorts)
+        r = moe_parallel(args.steps, warmup, world, rank, cohorts, args.exchange)
     line = {"metric": "fp8_moe_tflops", "value": r["flops"] / (r["ms"] * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
@@ -748,6 +753,8 @@ def main():
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
     else:
         line["rows_sent_rank0"] = r["rows_sent_rank0"]
+        line["config"]["exchange"] = ("rows written into the owner's memory over NVLink by this library's kernels" if r["exchange"] == "push"
+                                      else "NCCL all-to-all, equal splits")
         line["ep_parity"] = r["ep_parity"]
     if rank == 0:
         print(json.dumps(line), flush=True)

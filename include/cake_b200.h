@@ -225,7 +225,9 @@ int cake_b200_moe_launch(void* handle, void* cuda_stream);
 int cake_b200_moe_launch_stage(void* handle, int stage, void* cuda_stream);
 int cake_b200_moe_destroy(void* handle);
 /* Device pointers of intermediates inside the workspace, for tests and for expert-parallel callers:
- * which = 0 expert_ids int32 [T,top_k]; 1 route_weights fp32 [T,top_k]; 2 counts; 3 offsets; 4 sorted_pairs; 5 inv_perm. */
+ * which = 0 expert_ids int32 [T,top_k]; 1 route_weights fp32 [T,top_k]; 2 counts; 3 offsets; 4 sorted_pairs; 5 inv_perm;
+ * 6 the weighted contribution rows bf16 [T*top_k,H] that GEMM2 writes in sorted order (row inv_perm[t,slot] belongs to
+ *   token t's slot; the combine stage, or an expert-parallel caller, adds a token's rows in slot order). */
 int cake_b200_moe_intermediate(void* handle, int which, void** device_pointer_out);
 
 /* ------------------------------------------------------------------------------------------
@@ -390,6 +392,35 @@ size_t cake_b200_ep_row_bytes(const cake_b200_ep_config* config);
 int cake_b200_ep_exchange_create(void** buffers, const cake_b200_ep_config* config, void** handle_out);
 int cake_b200_ep_exchange_launch_stage(void* handle, int stage, void* cuda_stream);
 int cake_b200_ep_exchange_destroy(void* handle);
+
+/* ------------------------------------------------------------------------------------------
+ * The same exchange with the ranks writing straight into each other's memory over NVLink instead of through a
+ * collective library (no counterpart in the reference, which has no distributed layer).  Every rank owns one
+ * SYMMETRIC buffer of cake_b200_ep_push_symmetric_bytes(), zero-filled once, that the host has mapped into every
+ * other rank's address space (peer_bases[r] = where rank r's buffer is mapped HERE; peer_bases[rank] = this rank's
+ * own).  Only the rows that are needed travel; each side publishes a step number with a system-scope release
+ * when its rows are out, and the other side waits for it with a bounded wait (status word 5 on expiry).
+ * buffers: 0 expert_ids int32 [T,top_k], 1 route_weights fp32 [T,top_k], 2 hidden_states e4m3 [T,H],
+ *   3 hidden_states_scale fp32 [H/128,T] (this rank's tokens); 4 peer_bases uint64 [world] (device array);
+ *   5 this rank's symmetric buffer; 6 scratch of cake_b200_ep_push_scratch_bytes(), zero-filled once (its first word
+ *   is the status word); 7..10 the rank-local layer's inputs written by stage 1 (hidden e4m3 [world*capacity,H],
+ *   scales fp32 [H/128,world*capacity], expert_ids int32 and route_weights fp32 [world*capacity,top_k]; rows beyond
+ *   those received carry expert id -1); 11 the layer's contribution rows and 12 its inv_perm
+ *   (cake_b200_moe_intermediate 6 and 5; the layer runs its stages 0..2 only); 13 output bf16 [T,H].
+ * stages: 0 plan + push rows, 1 wait + unpack, 2 combine + push partial rows back, 3 wait + reduce.  All ranks must
+ * run the same sequence of steps; the kernels of a step on different GPUs wait for one another, so they must not
+ * share a GPU.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  int64_t tokens;   /* tokens of this rank */
+  int64_t capacity; /* rows a rank can receive from one source; >= the largest `tokens` of any rank */
+  int32_t hidden, top_k, world, experts, rank;
+} cake_b200_ep_push_config;
+size_t cake_b200_ep_push_symmetric_bytes(const cake_b200_ep_push_config* config);
+size_t cake_b200_ep_push_scratch_bytes(const cake_b200_ep_push_config* config);
+int cake_b200_ep_push_create(void** buffers, const cake_b200_ep_push_config* config, void** handle_out);
+int cake_b200_ep_push_launch_stage(void* handle, int stage, void* cuda_stream);
+int cake_b200_ep_push_destroy(void* handle);
 
 #ifdef __cplusplus
 }

@@ -69,6 +69,11 @@ class EpConfig(Structure):
                 ("world", c_int32), ("experts", c_int32)]
 
 
+class EpPushConfig(Structure):
+    _fields_ = [("tokens", c_int64), ("capacity", c_int64), ("hidden", c_int32), ("top_k", c_int32),
+                ("world", c_int32), ("experts", c_int32), ("rank", c_int32)]
+
+
 class GqaDecodeConfig(Structure):
     _fields_ = [("batch", c_int64), ("num_qo_heads", c_int32), ("num_kv_heads", c_int32), ("head_dim", c_int32),
                 ("page_size", c_int32), ("max_kv_len", c_int64)]
@@ -115,7 +120,8 @@ OPERATORS = {
 EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_test_hooks", "cake_b200_launch_facts", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
             "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit",
             "cake_b200_ep_row_bytes", "cake_b200_ep_exchange_create", "cake_b200_ep_exchange_launch_stage",
-            "cake_b200_ep_exchange_destroy"]
+            "cake_b200_ep_exchange_destroy", "cake_b200_ep_push_symmetric_bytes", "cake_b200_ep_push_scratch_bytes",
+            "cake_b200_ep_push_create", "cake_b200_ep_push_launch_stage", "cake_b200_ep_push_destroy"]
            + [f"cake_b200_{stem}_{verb}" for stem in OPERATORS for verb in ("create", "launch", "destroy")]
            + [f"cake_b200_{stem}_workspace_bytes" for stem, (_, ws) in OPERATORS.items() if ws])
 
@@ -144,6 +150,13 @@ def library() -> ctypes.CDLL:
         lib.cake_b200_ep_exchange_create.argtypes = [POINTER(c_void_p), POINTER(EpConfig), POINTER(c_void_p)]
         lib.cake_b200_ep_exchange_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
         lib.cake_b200_ep_exchange_destroy.argtypes = [c_void_p]
+        lib.cake_b200_ep_push_symmetric_bytes.argtypes = [POINTER(EpPushConfig)]
+        lib.cake_b200_ep_push_symmetric_bytes.restype = c_size_t
+        lib.cake_b200_ep_push_scratch_bytes.argtypes = [POINTER(EpPushConfig)]
+        lib.cake_b200_ep_push_scratch_bytes.restype = c_size_t
+        lib.cake_b200_ep_push_create.argtypes = [POINTER(c_void_p), POINTER(EpPushConfig), POINTER(c_void_p)]
+        lib.cake_b200_ep_push_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
+        lib.cake_b200_ep_push_destroy.argtypes = [c_void_p]
         for stem, (config, has_ws) in OPERATORS.items():
             create = getattr(lib, f"cake_b200_{stem}_create")
             create.argtypes = [POINTER(c_void_p), POINTER(config), POINTER(c_void_p)]

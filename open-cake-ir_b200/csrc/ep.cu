@@ -217,3 +217,371 @@ extern "C" int cake_b200_ep_exchange_destroy(void* handle) {
   delete static_cast<cake::ep::Handle*>(handle);
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// The same exchange without a collective library: ranks write straight into each other's memory.
+//
+// Every rank owns one SYMMETRIC buffer (the same layout on every rank, each mapped into every other rank's
+// address space by the host: torch.distributed._symmetric_memory, or any other peer mapping):
+//   flags block | recv [world, capacity, row_bytes] | returned [world, capacity, H] bf16
+// Dispatch: the rank that routed a token writes its packed row into the receive block of every rank that owns
+// one of its experts, with plain 16-byte stores over NVLink -- only the rows that are needed travel -- and,
+// once all of its rows are out, publishes the row count and a step number (the "epoch") in that rank's flags
+// block with a system-scope release.  The receiver waits for the epoch of every source (bounded: on expiry it
+// records a status and goes on with what it has), then compacts the rows it received into the rank-local
+// layer's inputs.  The way back is the mirror image: the owner of the experts adds a received row's local
+// contributions (slot order, fp32), rounds to bf16 and writes the row into the token owner's `returned`
+// block; the token owner waits for every rank's epoch and adds the partial rows in rank order.
+// No load or store here uses a cluster or multicast form; a peer's memory is only ever the target of plain
+// stores, and every wait is on a flag in the waiting GPU's own memory.
+namespace cake {
+namespace ep {
+
+constexpr int kMaxWorld = 64;
+constexpr size_t kFlagBytes = 1024;      // dispatch_flag[64] | dispatch_count[64] | return_flag[64] | spare
+__host__ __device__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+__host__ __device__ inline size_t recv_offset() { return kFlagBytes; }
+__host__ __device__ inline size_t returned_offset(int world, int cap, int hidden, int top_k) {
+  return kFlagBytes + align256(size_t(world) * cap * row_bytes(hidden, top_k));
+}
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+struct PushScratch {       // ints in the rank's own (non-symmetric) scratch, after the 256-byte status block
+  int* status;
+  int* epoch;              // [1] step number, bumped by the plan kernel
+  int* done;               // [2] CTA completion counters of the two push kernels
+  int* send_count;         // [world]
+  int* recv_total;         // [1] rows received this step
+  int* row_src;            // [rows] source rank of compacted row c
+  int* row_slot;           // [rows] its slot in that rank's block
+  int* slot_of;            // [T, world]
+};
+
+// One warp per destination rank: slots of the tokens that rank needs, in token order; the row count; and the epoch.
+__global__ void __launch_bounds__(32)
+push_plan_kernel(const int* __restrict__ expert_ids, PushScratch sc, int tokens, int top_k, int world, int experts_per_rank) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  const uint32_t below = (1u << lane) - 1u;
+  int cursor = 0;
+  for (int base = 0; base < tokens; base += 32) {
+    const int t = base + lane;
+    bool need = false;
+    if (t < tokens) {
+      for (int k = 0; k < top_k; ++k) {
+        const int e = expert_ids[size_t(t) * top_k + k];
+        need |= (e >= 0 && e / experts_per_rank == r);
+      }
+    }
+    const uint32_t mask = __ballot_sync(0xffffffffu, need);
+    if (t < tokens) sc.slot_of[size_t(t) * world + r] = need ? cursor + __popc(mask & below) : -1;
+    cursor += __popc(mask);
+  }
+  if (lane == 0) {
+    sc.send_count[r] = cursor;
+    if (r == 0) *sc.epoch = *sc.epoch + 1;
+  }
+}
+
+// After its own stores a CTA fences at system scope and counts itself; the last one publishes `values[r]`
+// (may be null) and the epoch in every peer's flags block.  Every thread of the CTA must call.
+__device__ __forceinline__ void publish_when_last(int* done, const unsigned long long* peer_bases, int world, int me, int epoch,
+                                                  const int* values, size_t count_off, size_t flag_off) {
+  __shared__ int is_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(done, 1) == int(gridDim.x) - 1;
+  __syncthreads();
+  if (!is_last) return;
+  if (threadIdx.x < world) {
+    uint8_t* peer = reinterpret_cast<uint8_t*>(peer_bases[threadIdx.x]);
+    if (values) st_relaxed_sys(reinterpret_cast<int*>(peer + count_off) + me, values[threadIdx.x]);
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(peer + flag_off) + me, epoch);
+  }
+  if (threadIdx.x == 0) *done = 0;               // ready for the next step
+}
+
+// One warp per (token, destination rank) with a slot: the packed row goes straight into that rank's receive block.
+__global__ void __launch_bounds__(256)
+push_dispatch_kernel(const uint8_t* __restrict__ hidden_states, const float* __restrict__ hidden_scale,
+                     const int* __restrict__ expert_ids, const float* __restrict__ route_weights, PushScratch sc,
+                     const unsigned long long* __restrict__ peer_bases, int tokens, int top_k, int world, int me, int capacity,
+                     int hidden) {
+  const int lane = threadIdx.x & 31;
+  const int w = row_bytes(hidden, top_k);
+  const int kb = hidden / 128;
+  for (int item = blockIdx.x * 8 + (threadIdx.x >> 5); item < tokens * world; item += gridDim.x * 8) {
+    const int t = item / world, r = item % world;
+    const int slot = sc.slot_of[item];
+    if (slot < 0) continue;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(peer_bases[r]) + recv_offset() + (size_t(me) * capacity + slot) * w;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden_states + size_t(t) * hidden);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int i = lane; i < hidden / 16; i += 32) d4[i] = __ldg(src + i);
+    float* ds = reinterpret_cast<float*>(dst + hidden);
+    for (int i = lane; i < kb; i += 32) ds[i] = __ldg(hidden_scale + size_t(i) * tokens + t);
+    int* di = reinterpret_cast<int*>(dst + hidden + 4 * kb);
+    float* dw = reinterpret_cast<float*>(dst + hidden + 4 * kb + 4 * top_k);
+    if (lane < top_k) {
+      di[lane] = expert_ids[size_t(t) * top_k + lane];
+      dw[lane] = route_weights[size_t(t) * top_k + lane];
+    }
+  }
+  publish_when_last(sc.done, peer_bases, world, me, *sc.epoch, sc.send_count, 64 * sizeof(int), 0);
+}
+
+// Waits (bounded) until every source's flag has reached this step's epoch; returns the counts in shared memory.
+__device__ __forceinline__ void wait_for_sources(const int* flags, const int* counts, int world, int epoch, int* status,
+                                                 int* cnt /* shared [kMaxWorld] */) {
+  if (threadIdx.x < world) {
+    const long long start = clock64();
+    bool ok = true;
+    while (ld_acquire_sys(flags + threadIdx.x) < epoch) {
+      if (clock64() - start > kWaitClockBudget) { ok = false; if (status) atomicCAS(status, 0, kStatusWaitFlag); break; }
+      __nanosleep(64);
+    }
+    cnt[threadIdx.x] = ok && counts ? counts[threadIdx.x] : 0;
+  }
+  __syncthreads();
+}
+
+// One warp per row of the rank-local layer's inputs: row c < total is the c-th received row (sources in rank
+// order, slots in order), anything beyond carries expert id -1.
+__global__ void __launch_bounds__(256)
+push_unpack_kernel(const uint8_t* __restrict__ own_base, PushScratch sc, uint8_t* __restrict__ hidden_states,
+                   float* __restrict__ hidden_scale, int* __restrict__ expert_ids, float* __restrict__ route_weights,
+                   int rows, int top_k, int world, int capacity, int hidden) {
+  __shared__ int cnt[kMaxWorld];
+  __shared__ int pre[kMaxWorld + 1];
+  const int lane = threadIdx.x & 31;
+  const int epoch = *sc.epoch;
+  wait_for_sources(reinterpret_cast<const int*>(own_base), reinterpret_cast<const int*>(own_base) + 64, world, epoch, sc.status, cnt);
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int r = 0; r < world; ++r) { pre[r] = run; run += min(cnt[r], capacity); }
+    pre[world] = run;
+    if (blockIdx.x == 0) *sc.recv_total = run;
+  }
+  __syncthreads();
+  const int total = pre[world];
+  const int w = row_bytes(hidden, top_k);
+  const int kb = hidden / 128;
+  for (int c = blockIdx.x * 8 + (threadIdx.x >> 5); c < rows; c += gridDim.x * 8) {
+    if (c >= total) {
+      if (lane < top_k) { expert_ids[size_t(c) * top_k + lane] = -1; route_weights[size_t(c) * top_k + lane] = 0.f; }
+      continue;
+    }
+    int src = 0;
+    while (src + 1 < world && c >= pre[src + 1]) ++src;
+    const int slot = c - pre[src];
+    const uint8_t* row = own_base + recv_offset() + (size_t(src) * capacity + slot) * w;
+    const int* si = reinterpret_cast<const int*>(row + hidden + 4 * kb);
+    const float* sw = reinterpret_cast<const float*>(row + hidden + 4 * kb + 4 * top_k);
+    if (lane < top_k) {
+      expert_ids[size_t(c) * top_k + lane] = si[lane];
+      route_weights[size_t(c) * top_k + lane] = sw[lane];
+    }
+    if (lane == 0) { sc.row_src[c] = src; sc.row_slot[c] = slot; }
+    const uint4* s4 = reinterpret_cast<const uint4*>(row);
+    uint4* d4 = reinterpret_cast<uint4*>(hidden_states + size_t(c) * hidden);
+    for (int i = lane; i < hidden / 16; i += 32) d4[i] = s4[i];
+    const float* ss = reinterpret_cast<const float*>(row + hidden);
+    for (int i = lane; i < kb; i += 32) hidden_scale[size_t(i) * rows + c] = ss[i];
+  }
+}
+
+// One CTA per received row: its local contributions (rows of y by inv_perm) added in slot order in fp32, rounded to
+// bf16 and written into the token owner's `returned` block.
+__global__ void __launch_bounds__(256)
+push_return_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv_perm, PushScratch sc,
+                   const unsigned long long* __restrict__ peer_bases, int world, int me, int capacity, int hidden, int top_k) {
+  __shared__ int rows_of[32];
+  const int c = blockIdx.x;
+  const int total = *sc.recv_total;
+  if (c < total) {
+    if (threadIdx.x < top_k) rows_of[threadIdx.x] = inv_perm[size_t(c) * top_k + threadIdx.x];
+    __syncthreads();
+    const int src = sc.row_src[c], slot = sc.row_slot[c];
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(peer_bases[src]) +
+                                                          returned_offset(world, capacity, hidden, top_k)) +
+                         (size_t(me) * capacity + slot) * hidden;
+    for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < top_k; ++s) {
+        const int row = rows_of[s];
+        if (row < 0) continue;
+        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + size_t(row) * hidden + col));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(dst + col) = o;
+    }
+  }
+  publish_when_last(sc.done + 1, peer_bases, world, me, *sc.epoch, nullptr, 0, 128 * sizeof(int));
+}
+
+// out[t,:] = bf16( sum over ranks r with a slot, in rank order, of returned[r, slot_of[t,r], :] ), once every rank's
+// partial rows of this step have landed.
+__global__ void __launch_bounds__(256)
+push_reduce_kernel(const uint8_t* __restrict__ own_base, PushScratch sc, __nv_bfloat16* __restrict__ out, int world, int capacity,
+                   int hidden, int top_k) {
+  __shared__ int cnt[kMaxWorld];
+  __shared__ int slots[kMaxWorld];
+  wait_for_sources(reinterpret_cast<const int*>(own_base) + 128, nullptr, world, *sc.epoch, sc.status, cnt);
+  const int t = blockIdx.x;
+  if (threadIdx.x < world) slots[threadIdx.x] = sc.slot_of[size_t(t) * world + threadIdx.x];
+  __syncthreads();
+  const __nv_bfloat16* returned = reinterpret_cast<const __nv_bfloat16*>(own_base + returned_offset(world, capacity, hidden, top_k));
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const int slot = slots[r];
+      if (slot < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(returned + (size_t(r) * capacity + slot) * hidden + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + size_t(t) * hidden + c) = o;
+  }
+}
+
+struct PushHandle {
+  int device;
+  cake_b200_ep_push_config cfg;
+  void* b[14];
+  PushScratch sc;
+};
+
+inline size_t push_scratch_bytes(const cake_b200_ep_push_config& c) {
+  const size_t rows = size_t(c.world) * c.capacity;
+  return 256 + align256(sizeof(int) * (8 + kMaxWorld)) + 2 * align256(rows * sizeof(int)) + align256(size_t(c.tokens) * c.world * sizeof(int));
+}
+
+}  // namespace ep
+}  // namespace cake
+
+static bool ep_push_config_ok(const cake_b200_ep_push_config& c) {
+  cake_b200_ep_config base{c.tokens, c.capacity, c.hidden, c.top_k, c.world, c.experts};
+  return ep_config_ok(base) && c.rank >= 0 && c.rank < c.world && c.world <= cake::ep::kMaxWorld && c.capacity <= (1 << 22);
+}
+
+extern "C" size_t cake_b200_ep_push_symmetric_bytes(const cake_b200_ep_push_config* c) {
+  if (!c || !ep_push_config_ok(*c)) return 0;
+  return cake::ep::returned_offset(c->world, int(c->capacity), c->hidden, c->top_k) + size_t(c->world) * c->capacity * c->hidden * 2;
+}
+
+extern "C" size_t cake_b200_ep_push_scratch_bytes(const cake_b200_ep_push_config* c) {
+  return c && ep_push_config_ok(*c) ? cake::ep::push_scratch_bytes(*c) : 0;
+}
+
+extern "C" int cake_b200_ep_push_create(void** buffers, const cake_b200_ep_push_config* config, void** handle_out) {
+  using namespace cake;
+  if (!buffers || !config || !handle_out) return kErrBadArgument;
+  *handle_out = nullptr;
+  int device = 0;
+  if (int rc = require_blackwell(&device)) return rc;
+  if (!ep_push_config_ok(*config)) return kErrBadArgument;
+  for (int i = 0; i < 14; ++i)
+    if (!buffers[i] || (reinterpret_cast<uintptr_t>(buffers[i]) & 15)) return kErrBadArgument;
+  if (reinterpret_cast<uintptr_t>(buffers[5]) & 255) return kErrBadArgument;     // the symmetric buffer and the scratch are 256-byte aligned
+  if (reinterpret_cast<uintptr_t>(buffers[6]) & 255) return kErrBadArgument;
+  auto* h = new (std::nothrow) ep::PushHandle;
+  if (!h) return int(cudaErrorMemoryAllocation);
+  h->device = device;
+  h->cfg = *config;
+  for (int i = 0; i < 14; ++i) h->b[i] = buffers[i];
+  uint8_t* s = static_cast<uint8_t*>(buffers[6]);
+  const size_t rows = size_t(config->world) * config->capacity;
+  ep::PushScratch& sc = h->sc;
+  sc.status = reinterpret_cast<int*>(s);
+  int* words = reinterpret_cast<int*>(s + 256);
+  sc.epoch = words;
+  sc.done = words + 1;
+  sc.recv_total = words + 3;
+  sc.send_count = words + 8;
+  s += 256 + ep::align256(sizeof(int) * (8 + ep::kMaxWorld));
+  sc.row_src = reinterpret_cast<int*>(s);
+  s += ep::align256(rows * sizeof(int));
+  sc.row_slot = reinterpret_cast<int*>(s);
+  s += ep::align256(rows * sizeof(int));
+  sc.slot_of = reinterpret_cast<int*>(s);
+  *handle_out = h;
+  return 0;
+}
+
+extern "C" int cake_b200_ep_push_launch_stage(void* handle, int stage, void* cuda_stream) {
+  using namespace cake;
+  if (!handle) return kErrBadArgument;
+  auto* h = static_cast<ep::PushHandle*>(handle);
+  int device = -1;
+  CAKE_CUDA_OK(cudaGetDevice(&device));
+  if (device != h->device) return kErrWrongDevice;
+  const cake_b200_ep_push_config& c = h->cfg;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const int tokens = int(c.tokens), cap = int(c.capacity), rows = c.world * cap;
+  auto* ids = static_cast<const int*>(h->b[0]);
+  auto* weights = static_cast<const float*>(h->b[1]);
+  auto* hidden = static_cast<const uint8_t*>(h->b[2]);
+  auto* scale = static_cast<const float*>(h->b[3]);
+  auto* peers = static_cast<const unsigned long long*>(h->b[4]);
+  auto* own = static_cast<const uint8_t*>(h->b[5]);
+  switch (stage) {
+    case 0: {  // plan + dispatch: this rank's rows go into their owners' receive blocks
+      ep::push_plan_kernel<<<c.world, 32, 0, s>>>(ids, h->sc, tokens, c.top_k, c.world, c.experts / c.world);
+      const int blocks = tokens > 0 ? (tokens * c.world + 7) / 8 : 1;
+      ep::push_dispatch_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(hidden, scale, ids, weights, h->sc, peers, tokens, c.top_k,
+                                                                           c.world, c.rank, cap, c.hidden);
+      break;
+    }
+    case 1: {  // wait for every source, then compact the received rows into the rank-local layer's inputs
+      const int blocks = (rows + 7) / 8;
+      ep::push_unpack_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(own, h->sc, static_cast<uint8_t*>(h->b[7]),
+                                                                         static_cast<float*>(h->b[8]), static_cast<int*>(h->b[9]),
+                                                                         static_cast<float*>(h->b[10]), rows, c.top_k, c.world, cap, c.hidden);
+      break;
+    }
+    case 2:    // combine the local contributions of every received row and write it back to the token's owner
+      ep::push_return_kernel<<<rows, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(h->b[11]), static_cast<const int*>(h->b[12]), h->sc,
+                                                  peers, c.world, c.rank, cap, c.hidden, c.top_k);
+      break;
+    case 3:    // wait for every rank's partial rows, then add them in rank order
+      if (tokens > 0)
+        ep::push_reduce_kernel<<<tokens, 256, 0, s>>>(own, h->sc, static_cast<__nv_bfloat16*>(h->b[13]), c.world, cap, c.hidden, c.top_k);
+      break;
+    default:
+      return kErrBadArgument;
+  }
+  return int(cudaGetLastError());
+}
+
+extern "C" int cake_b200_ep_push_destroy(void* handle) {
+  delete static_cast<cake::ep::PushHandle*>(handle);
+  return 0;
+}

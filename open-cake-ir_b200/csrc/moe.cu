@@ -637,6 +637,7 @@ extern "C" int cake_b200_moe_intermediate(void* handle, int which, void** out) {
     case 3: *out = h->ws + l.offsets; break;
     case 4: *out = h->ws + l.sorted_pairs; break;
     case 5: *out = h->ws + l.inv_perm; break;
+    case 6: *out = h->ws + l.y; break;
     default: return kErrBadArgument;
   }
   return 0;

@@ -290,3 +290,123 @@ class NativeExpertParallelMoe:
             self._lib.library().cake_b200_ep_exchange_destroy(self._handle)
             import ctypes
             self._handle = ctypes.c_void_p()
+
+
+class PushExpertParallelMoe:
+    """The expert-parallel layer with the exchange done by the ranks' own kernels over NVLink
+    (``cake_b200_ep_push_*``): a rank writes each needed row straight into the receive block of the rank that owns
+    the expert, and each partial row straight back into the token owner's block, inside one symmetric buffer per
+    rank that ``torch.distributed._symmetric_memory`` maps into every peer.  No collective call is left in a step,
+    only the needed rows travel, and the rank-local layer sees the received rows compacted.  A step is
+    route -> plan + push -> wait + unpack -> layer stages 0..2 -> combine + push back -> wait + reduce, all on the
+    caller's stream; ``capture()`` records it as one CUDA graph.  Same constructor as ``NativeExpertParallelMoe``.
+    With a world of one the symmetric buffer is an ordinary tensor and the rank pushes to itself."""
+
+    STEP_PARTS = ("route_plan_push", "wait_unpack", "layer_route_permute_gather", "layer_gemm1_swiglu", "layer_gemm2",
+                  "combine_push_back", "wait_reduce")
+
+    def __init__(self, weights: dict, routing_logits, routing_bias, hidden_states, hidden_states_scale, *,
+                 experts: int, top_k: int = 8, routing: str = "softmax", n_group: int = 8, topk_group: int = 4,
+                 act_mode: str = "fp8", group=None):
+        import ctypes
+
+        from . import _lib, ops
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        dev = hidden_states.device
+        self.device = dev
+        tokens, hidden = hidden_states.shape
+        self.tokens, self.hidden, self.top_k = tokens, hidden, top_k
+        cap = tokens
+        rows = self.world * cap
+        cfg = _lib.EpPushConfig(tokens, cap, hidden, top_k, self.world, experts, self.rank)
+        lib = _lib.library()
+        sym_bytes = int(lib.cake_b200_ep_push_symmetric_bytes(ctypes.byref(cfg)))
+        if sym_bytes == 0:
+            raise ValueError("unsupported expert-parallel configuration (hidden must be a multiple of 512 and top_k even)")
+        i32, f32 = torch.int32, torch.float32
+        with torch.cuda.device(dev):
+            if self.world > 1:
+                import torch.distributed._symmetric_memory as symm
+                self.symmetric = symm.empty(sym_bytes, dtype=torch.uint8, device=dev)
+                self.symmetric.zero_()
+                torch.cuda.synchronize(dev)
+                self._symm_handle = symm.rendezvous(self.symmetric, group=dist.group.WORLD if group is None else group)
+                bases = [int(p) for p in self._symm_handle.buffer_ptrs]
+            else:
+                self.symmetric = torch.zeros(sym_bytes + 256, dtype=torch.uint8, device=dev)
+                bases = [(self.symmetric.data_ptr() + 255) // 256 * 256]
+            self.peer_bases = torch.tensor(bases, dtype=torch.int64, device=dev)
+            self.scratch = torch.zeros(int(lib.cake_b200_ep_push_scratch_bytes(ctypes.byref(cfg))) + 256, dtype=torch.uint8, device=dev)
+            self.scratch_ptr = (self.scratch.data_ptr() + 255) // 256 * 256
+        self.ids = torch.empty((tokens, top_k), dtype=i32, device=dev)
+        self.route_weights = torch.empty((tokens, top_k), dtype=f32, device=dev)
+        self.recv_hidden = torch.zeros((rows, hidden), dtype=torch.float8_e4m3fn, device=dev)
+        self.recv_scale = torch.zeros((hidden // 128, rows), dtype=f32, device=dev)
+        self.recv_ids = torch.full((rows, top_k), -1, dtype=i32, device=dev)
+        self.recv_weights = torch.zeros((rows, top_k), dtype=f32, device=dev)
+        self.partial = torch.empty((rows, hidden), dtype=torch.bfloat16, device=dev)     # the layer's own output: unused (stage 3 is not run)
+        self.output = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        self.router = ops.MoeRouting(routing_logits, routing_bias, weights["routed_scaling_factor"], self.ids,
+                                     self.route_weights, top_k=top_k, n_group=n_group, topk_group=topk_group, mode=routing)
+        layer_inputs = dict(weights)
+        layer_inputs.update(expert_ids=self.recv_ids, route_weights=self.recv_weights, hidden_states=self.recv_hidden,
+                            hidden_states_scale=self.recv_scale)
+        self.layer = ops.Fp8Moe(layer_inputs, self.partial, experts=experts, top_k=top_k, act_mode=act_mode, external_routing=True)
+        contributions, inv_perm = self.layer.intermediate("contributions"), self.layer.intermediate("inv_perm")
+        own = bases[self.rank] if self.world > 1 else bases[0]
+        pointers = [self.ids.data_ptr(), self.route_weights.data_ptr(), hidden_states.data_ptr(), hidden_states_scale.data_ptr(),
+                    self.peer_bases.data_ptr(), own, self.scratch_ptr, self.recv_hidden.data_ptr(), self.recv_scale.data_ptr(),
+                    self.recv_ids.data_ptr(), self.recv_weights.data_ptr(), contributions.data_ptr(), inv_perm.data_ptr(),
+                    self.output.data_ptr()]
+        self._keep = [hidden_states, hidden_states_scale, contributions, inv_perm]
+        array = (ctypes.c_void_p * len(pointers))(*pointers)
+        self._handle = ctypes.c_void_p()
+        with torch.cuda.device(dev):
+            code = lib.cake_b200_ep_push_create(array, ctypes.byref(cfg), ctypes.byref(self._handle))
+        if code:
+            raise _lib.CakeError("cake_b200_ep_push_create", code)
+        self._lib = _lib
+        if self.world > 1:
+            dist.barrier(group)            # every rank's buffers are zeroed and mapped before anyone pushes
+        # kernels of this library launched per step: routing 1, exchange 6, rank-local layer stages 0..2: 6
+        self.launches_per_step = 13
+        self.slot_of = None
+
+    def _stage(self, stage: int):
+        code = self._lib.library().cake_b200_ep_push_launch_stage(self._handle, stage, torch.cuda.current_stream().cuda_stream)
+        if code:
+            raise self._lib.CakeError("cake_b200_ep_push_launch_stage", code)
+
+    def _parts(self):
+        def route_plan_push():
+            self.router.launch()
+            self._stage(0)
+        return [route_plan_push, lambda: self._stage(1), lambda: self.layer.launch_stage(0), lambda: self.layer.launch_stage(1),
+                lambda: self.layer.launch_stage(2), lambda: self._stage(2), lambda: self._stage(3)]
+
+    def _eager(self) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            for part in self._parts():
+                part()
+        return self.output
+
+    capture = NativeExpertParallelMoe.capture
+    forward = NativeExpertParallelMoe.forward
+    stage_times = NativeExpertParallelMoe.stage_times
+
+    def status(self) -> int:
+        """0, or 5 when a wait for another rank's rows ran out (synchronises the stream)."""
+        with torch.cuda.device(self.device):
+            return self._lib.read_status(self.scratch_ptr, torch.cuda.current_stream().cuda_stream)
+
+    def rows_sent(self) -> int:
+        words = self.scratch[self.scratch_ptr - self.scratch.data_ptr() + 256:][:4 * (8 + 64)].view(torch.int32)
+        return int(words[8:8 + self.world].sum().item())
+
+    def close(self):
+        if self._handle.value:
+            self._lib.library().cake_b200_ep_push_destroy(self._handle)
+            import ctypes
+            self._handle = ctypes.c_void_p()

@@ -265,18 +265,21 @@ class Fp8Moe(_Operator):
             raise _lib.CakeError("cake_b200_moe_launch_stage", code)
 
     def intermediate(self, name: str) -> torch.Tensor:
-        """Device view of an intermediate in the workspace (expert_ids, route_weights, counts,
-        offsets, sorted_pairs, inv_perm) -- valid after a launch has completed."""
+        """Device view of an intermediate in the workspace (expert_ids, route_weights, counts, offsets,
+        sorted_pairs, inv_perm, contributions) -- contents are valid after a launch has completed."""
         import ctypes
-        which = ["expert_ids", "route_weights", "counts", "offsets", "sorted_pairs", "inv_perm"].index(name)
+        which = ["expert_ids", "route_weights", "counts", "offsets", "sorted_pairs", "inv_perm", "contributions"].index(name)
         ptr = ctypes.c_void_p()
         code = _lib.library().cake_b200_moe_intermediate(self.native.handle, which, ctypes.byref(ptr))
         if code:
             raise _lib.CakeError("cake_b200_moe_intermediate", code)
         pairs = self.tokens * self.top_k
+        offset = ptr.value - self.workspace.data_ptr()
+        if name == "contributions":
+            nbytes = pairs * self.config.hidden * 2
+            return self.workspace[offset:offset + nbytes].view(torch.bfloat16).view(pairs, self.config.hidden)
         count = {"counts": self.local_experts, "offsets": self.local_experts + 1}.get(name, pairs)
         dtype = torch.float32 if name == "route_weights" else torch.int32
-        offset = ptr.value - self.workspace.data_ptr()
         if not 0 <= offset <= self.workspace.numel() - count * 4:
             raise RuntimeError(f"{name} is not inside the workspace (routing is external)")
         return self.workspace[offset:offset + count * 4].view(dtype)

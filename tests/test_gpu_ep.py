@@ -35,11 +35,17 @@ def _worker(rank, world, port, results, native):
                                         routing="softmax", device=f"cuda:{rank}", gen_device="cpu",
                                         first_token=rank * t_local, total_tokens=TOKENS)
         args = [dev[k] for k in ("routing_logits", "routing_bias", "routed_scaling_factor", "hidden_states", "hidden_states_scale")]
-        if native:
-            layer = ep.NativeExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
-                                               dev["hidden_states_scale"], experts=SHAPE["experts"], routing="softmax")
-            for _ in range(2):      # twice: buffers are reused between steps
+        if native in ("native", "push"):
+            cls = ep.NativeExpertParallelMoe if native == "native" else ep.PushExpertParallelMoe
+            layer = cls(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                        dev["hidden_states_scale"], experts=SHAPE["experts"], routing="softmax")
+            for _ in range(3):      # several steps: buffers, flags and step numbers are reused between steps
                 out = layer.forward()
+            if native == "push":
+                assert layer.status() == 0
+                layer.capture()     # and once more as a CUDA graph
+                out = layer.forward()
+                assert layer.status() == 0
         else:
             route_factory, local_layer = ep.native_layer(dev, capacity=TOKENS, experts=SHAPE["experts"], device=f"cuda:{rank}")
             layer = ep.ExpertParallelMoe(experts=SHAPE["experts"], top_k=8, hidden=SHAPE["hidden"], capacity=TOKENS,
@@ -53,7 +59,7 @@ def _worker(rank, world, port, results, native):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("native", [True, False], ids=["native-exchange", "torch-exchange"])
+@pytest.mark.parametrize("native", ["native", "push", "torch"], ids=["nccl-exchange", "push-exchange", "torch-exchange"])
 def test_two_rank_layer_equals_single_gpu_layer(native):
     world = 2
     results = mp.Manager().dict()
@@ -79,3 +85,23 @@ def test_single_rank_exchange_is_the_identity():
     torch.cuda.synchronize()
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     assert int((layer.slot_of.cpu()[:, 0] != torch.arange(200)).sum()) == 0
+
+
+def test_single_rank_push_exchange_is_the_identity():
+    """The push exchange with a world of one: the rank writes its rows into its own receive block, waits for its own
+    flags, and must reproduce the plain layer bit for bit over several steps (flags and step numbers are reused)."""
+    dev = cake.workloads.moe_inputs(tokens=200, **SHAPE, local_experts=SHAPE["experts"], local_offset=0, routing="softmax",
+                                    device="cuda", gen_device="cpu")
+    want = cake.fp8_moe(dev, experts=SHAPE["experts"], routing="softmax", act_mode="fp8")
+    layer = ep.PushExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                                     dev["hidden_states_scale"], experts=SHAPE["experts"], routing="softmax")
+    for _ in range(3):
+        got = layer.forward()
+        torch.cuda.synchronize()
+        assert layer.status() == 0
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert layer.rows_sent() == 200
+    layer.capture()
+    got = layer.forward()
+    torch.cuda.synchronize()
+    assert layer.status() == 0 and torch.equal(got.view(torch.int16), want.view(torch.int16))

@@ -37,7 +37,7 @@ def test_gemm_wait_runs_out_and_the_handle_stays_usable(hooks):
 
 
 def test_mla_decode_wait_runs_out_and_the_handle_stays_usable(hooks):
-    cpu, meta = cake.workloads.mla_decode_inputs(2, 128, 64, (600, 900), device="cpu")
+    cpu, meta = cake.workloads.mla_decode_inputs(2, 128, 64, (6000, 9000), device="cpu")      # every CTA meets three tiles or more
     dev = {k: v.cuda() for k, v in cpu.items()}
     out = torch.zeros_like(dev["q_nope"]); lse = torch.zeros((2, 128), dtype=torch.float32, device="cuda")
     op = cake.MlaPagedDecode(dev["q_nope"], dev["q_pe"], dev["ckv_cache"], dev["kpe_cache"], dev["kv_indptr"], dev["kv_indices"],
