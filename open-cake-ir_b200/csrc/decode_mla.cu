@@ -45,9 +45,9 @@ constexpr int kDimsPerCta = 256;                           // output dims per CT
 constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, tile range)
 constexpr int kQTmemSlabs = 5;                             // Q dims 0..319 live in tensor memory,
 constexpr int kQSmemSlabs = kSlabs - kQTmemSlabs;          //   dims 320..575 (four slabs) in shared memory
-constexpr int kQTmemCols = kQTmemSlabs * 32;               // 192 columns, two bf16 per column
+constexpr int kQTmemCols = kQTmemSlabs * 32;               // 160 columns, two bf16 per column
 constexpr int kQSlabBytes = kHeads * 128;                  // 16 KiB
-constexpr int kQSmemBytes = kQSmemSlabs * kQSlabBytes;     // 48 KiB
+constexpr int kQSmemBytes = kQSmemSlabs * kQSlabBytes;     // 64 KiB
 constexpr int kQStageRow = kQTmemSlabs * 128;              // 768 bytes of a Q row pass through the staging area
 constexpr int kTile = 32;                                  // tokens per tile
 constexpr int kStages = 4;                                 // ring stages
@@ -60,6 +60,8 @@ constexpr int kSoftmaxWarps = 8;                           //   (warp - 8) / 4 =
 constexpr int kThreads = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;                   // log2 units
+constexpr int kOutRowFloats = 36;                          // write-out: a row of 32 fp32 columns + 16 bytes of padding
+static_assert(kSoftmaxWarps * 32 * kOutRowFloats * 4 <= kKvStageBytes, "the write-out blocks must fit in ring stage 0");
 // tensor-memory columns: O fp32 (256), S fp32 (32), two P buffers of two bf16 terms each (2 x 32), Q dims 0..319
 // (160): all 512
 constexpr uint32_t kColO = 0, kColS = kColO + kDimsPerCta, kColP = kColS + kTile, kColQ = kColP + 2 * kTile, kTmemColumns = 512;
@@ -100,6 +102,7 @@ struct Shared {
 };
 
 constexpr size_t kSmemBytes = size_t(kQSmemBytes) + size_t(kStages) * kKvStageBytes + sizeof(Shared) + 1024;
+static_assert(kSmemBytes <= 232448, "the kernel's shared memory exceeds what a CTA may have on sm_100");
 
 __device__ __forceinline__ int seq_len(const Params& p, int b) {
   if (p.sparse_indices) return p.top_k;            // listed entries, some of which may be -1
@@ -467,17 +470,29 @@ mla_decode_kernel(const Params p) {
       const float total = sh->l_part[0][r] + sh->l_part[1][r];
       const float inv = (SPARSE && total == 0.f) ? 0.f : 1.f / total;        // sparse: no entry present in this range
       const size_t slot = size_t(slot_index) * p.heads + (head < p.heads ? head : 0);
-      float* dst = p.part_o + slot * kCkv + dq * kDimsPerCta;
+      // O leaves through shared memory (ring stage 0: every product of the pass has completed), so that a store
+      // instruction of a warp writes four whole 128-byte lines instead of 16 bytes of each of 32 rows: a warp
+      // transposes 32 rows x 32 columns at a time in a block of its own (rows 144 bytes apart: 16-byte accesses of
+      // eight consecutive rows, and of eight consecutive chunks of one row, meet no bank conflict).
+      float* scratch = reinterpret_cast<float*>(base + kQSmemBytes) + (warp - kSoftmaxWarp0) * (32 * kOutRowFloats);
+      const int first_head = head0 + quad * 32;                      // head of this warp's row 0
+      float* dst = p.part_o + (size_t(slot_index) * p.heads + first_head) * kCkv + dq * kDimsPerCta;
 #pragma unroll 1
       for (int c = grp * kOwnCols; c < (grp + 1) * kOwnCols; c += 32) {
         float o[32];
         tmem_ld_32x32b_x32(lane_base + kColO + c, o);
         tcgen05_wait_ld();
-        if (head < p.heads) {
 #pragma unroll
-          for (int k = 0; k < 32; k += 4)
-            *reinterpret_cast<float4*>(dst + c + k) = make_float4(o[k] * inv, o[k + 1] * inv, o[k + 2] * inv, o[k + 3] * inv);
+        for (int k = 0; k < 32; k += 4)
+          *reinterpret_cast<float4*>(scratch + lane * kOutRowFloats + k) = make_float4(o[k] * inv, o[k + 1] * inv, o[k + 2] * inv, o[k + 3] * inv);
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + (lane >> 3), cc = (lane & 7) * 4;
+          const float4 v = *reinterpret_cast<const float4*>(scratch + rr * kOutRowFloats + cc);
+          if (first_head + rr < p.heads) *reinterpret_cast<float4*>(dst + size_t(rr) * kCkv + c + cc) = v;
         }
+        __syncwarp();
       }
       if (dq == 0 && grp == 0 && head < p.heads) p.part_lse[slot] = (SPARSE && total == 0.f) ? -INFINITY : m_ref + log2f(total);
     }
