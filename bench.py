@@ -415,6 +415,20 @@ def moe_parallel(steps, warmup, world, rank, cohorts, exchange):
     dev = cake.workloads.moe_inputs(tokens=t_local, hidden=SHAPE["hidden"], inter=SHAPE["inter"], experts=SHAPE["experts"],
                                     local_experts=e_local, local_offset=rank * e_local, routing="softmax", device="cuda",
                                     gen_device="cuda", first_token=rank * t_local, total_tokens=SHAPE["tokens"])
+    if exchange == "push":
+        # the push exchange needs memory every rank can write; where the box cannot give it on every rank the NCCL
+        # exchange of this library's pack/unpack kernels is used instead, and the line says so
+        try:
+            import torch.distributed._symmetric_memory as symm
+            probe = symm.empty(4096, dtype=torch.uint8, device="cuda")
+            have = 1 if len(symm.rendezvous(probe, group=dist.group.WORLD).buffer_ptrs) == world else 0
+        except Exception as error:                      # noqa: BLE001 - any failure means "not available here"
+            print(f"bench: symmetric memory unavailable on rank {rank}: {error!r}", file=sys.stderr, flush=True)
+            have = 0
+        flag = torch.tensor([have], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            exchange = "nccl"
     layer_class = ep.PushExpertParallelMoe if exchange == "push" else ep.NativeExpertParallelMoe
     layer = layer_class(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
                         dev["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"], routing="softmax")
