@@ -501,7 +501,7 @@ def per_gpu_operators(peaks, with_cpu=True):
     from HBM), between one pair of events; algorithmic bytes or flops over the mean launch time.  Each row
     also carries the oracle timed on the host cores over a bounded sample of the same workload."""
     import open_cake_ir_b200 as cake
-    from oracle import attention as oracle_attention, block_scaled_gemm as oracle_gemm, rmsnorm as oracle_rmsnorm
+    from oracle import add_rmsnorm as oracle_add_rmsnorm, attention as oracle_attention, block_scaled_gemm as oracle_gemm, rmsnorm as oracle_rmsnorm
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     rows = []
@@ -526,7 +526,26 @@ def per_gpu_operators(peaks, with_cpu=True):
         row["cpu_baseline"] = {"value": nbytes / seconds / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                                "sample": f"the whole 4096x4096 problem, fp64 torch restatement (oracle/rmsnorm.py), {runs} run(s)"}
     rows.append(row)
-    del sets
+
+    # ---- two-output add + RMSNorm: 134 MB per launch; the six inputs above serve as delta / residual of three sets ----
+    add_sets = []
+    for k in range(3):
+        delta, residual, weight = sets[2 * k][0]["x"], sets[2 * k + 1][0]["x"], sets[2 * k][0]["weight"]
+        out, residual_out = torch.empty_like(delta), torch.empty_like(delta)
+        add_sets.append((out, residual_out, cake.AddRmsNorm(delta, residual, weight, out, residual_out, 1e-6)))
+    ms, stats, launches = time_rotating([op.launch for _, _, op in add_sets])
+    nbytes = 4 * 4096 * 4096 * 2 + 4096 * 2
+    row = {"operator": "add_rmsnorm", "workload": "delta, residual bf16 [4096,4096] -> out, residual_out; eps 1e-6", "ms": ms,
+           "samples": stats, "launches_timed": launches, "bound": "hbm", "unit": "GB/s", "achieved": nbytes / ms / 1e6,
+           "peak": peaks["hbm_gbs"], "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+           "l2": "three buffer sets of 134 MB in rotation (403 MB > 2 x L2)"}
+    if with_cpu:
+        d, r, w = sets[0][0]["x"].cpu(), sets[1][0]["x"].cpu(), sets[0][0]["weight"].cpu()
+        seconds, runs = _timed_cpu(lambda: oracle_add_rmsnorm.add_rmsnorm_reference(d, r, w, 1e-6))
+        row["cpu_baseline"] = {"value": nbytes / seconds / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                               "sample": f"the whole 4096x4096 problem, torch restatement (oracle/add_rmsnorm.py), {runs} run(s)"}
+    rows.append(row)
+    del sets, add_sets
 
     # ---- block-scaled GEMM: 155 MB per launch, three buffer sets ----
     sets = []

@@ -72,6 +72,15 @@ int cake_b200_launch_facts(const char* kernel, int* threads_per_cta, int* dynami
  * set.  Process-wide host state. */
 int cake_b200_test_hooks(int wait_budget_kiloclocks, int skip_load);
 
+/* Test accessor: where the plan kernel of a decode handle (kind "gqa_decode" or "mla_decode", the handle of the
+ * matching _create) leaves the work plan of its latest launch, as a device pointer into the caller's workspace.
+ *   gqa_decode: which 0 = pieces, int32 x4 each {sequence | pieces of it << 16, first token, list index of the
+ *               sequence's first piece, end token}, count = capacity; 1 = list index of each range's first piece
+ *               (INT_MAX where a range is empty); 2 = pieces per range; count = ranges.
+ *   mla_decode: which 0 = units (tiles + start-up shares) before each sequence, int32 [batch + 1];
+ *               which 1 = no pointer, count = the number of equal ranges the unit list is cut into. */
+int cake_b200_decode_plan_view(const char* kind, void* handle, int which, void** device_pointer_out, int* count_out);
+
 /* ------------------------------------------------------------------------------------------
  * RMSNorm.  Replaces the emitted RMSNorm starter (src/open_cake_ir/tasks/solx_fib/authoring.py:9-53)
  * for the operator defined at src/open_cake_ir/tasks/solx_fib/workload.py:214-218, :334-358:

@@ -117,7 +117,7 @@ OPERATORS = {
     "mla_prefill": (MlaPrefillConfig, True),
 }
 # every symbol include/cake_b200.h declares
-EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_test_hooks", "cake_b200_launch_facts", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
+EXPORTS = (["cake_b200_abi_version", "cake_b200_read_status", "cake_b200_test_hooks", "cake_b200_launch_facts", "cake_b200_decode_plan_view", "cake_b200_moe_intermediate", "cake_b200_moe_launch_stage",
             "cake_b200_gqa_decode_noalloc", "cake_b200_gqa_decode_noalloc_scratch_limit",
             "cake_b200_ep_row_bytes", "cake_b200_ep_exchange_create", "cake_b200_ep_exchange_launch_stage",
             "cake_b200_ep_exchange_destroy", "cake_b200_ep_push_symmetric_bytes", "cake_b200_ep_push_scratch_bytes",
@@ -140,6 +140,7 @@ def library() -> ctypes.CDLL:
         lib.cake_b200_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
         lib.cake_b200_test_hooks.argtypes = [c_int, c_int]
         lib.cake_b200_launch_facts.argtypes = [ctypes.c_char_p, POINTER(c_int), POINTER(c_int)]
+        lib.cake_b200_decode_plan_view.argtypes = [ctypes.c_char_p, c_void_p, c_int, POINTER(c_void_p), POINTER(c_int)]
         lib.cake_b200_moe_intermediate.argtypes = [c_void_p, c_int, POINTER(c_void_p)]
         lib.cake_b200_moe_launch_stage.argtypes = [c_void_p, c_int, c_void_p]
         lib.cake_b200_gqa_decode_noalloc.argtypes = [POINTER(c_void_p), POINTER(GqaDecodeConfig), c_void_p]
@@ -177,6 +178,16 @@ def library() -> ctypes.CDLL:
 
 def workspace_bytes(stem: str, config) -> int:
     return int(getattr(library(), f"cake_b200_{stem}_workspace_bytes")(ctypes.byref(config)))
+
+
+def decode_plan_view(stem: str, handle, which: int) -> tuple[int, int]:
+    """(device pointer, element count) of part ``which`` of the work plan a decode handle's plan kernel writes
+    (``cake_b200_decode_plan_view``; a test accessor)."""
+    pointer, count = c_void_p(), c_int()
+    code = library().cake_b200_decode_plan_view(stem.encode(), handle, which, ctypes.byref(pointer), ctypes.byref(count))
+    if code != 0:
+        raise CakeError("cake_b200_decode_plan_view", code)
+    return int(pointer.value or 0), int(count.value)
 
 
 class NativeHandle:

@@ -104,6 +104,9 @@ inline int require_blackwell(int* device_out) {
 void gemm_launch_facts(int* threads, int* dynamic_shared_bytes);
 void gqa_decode_launch_facts(int* threads, int* dynamic_shared_bytes);
 void mla_decode_launch_facts(int* threads, int* dynamic_shared_bytes);
+// Test accessors: where a decode handle's plan kernel leaves the work plan (device pointers into the workspace).
+int gqa_decode_plan_view(void* handle, int which, void** device_pointer_out, int* count_out);
+int mla_decode_plan_view(void* handle, int which, void** device_pointer_out, int* count_out);
 
 inline int sm_count(int device) {
   int n = 148;

@@ -596,6 +596,19 @@ inline int launch(Params& p, int sms, cudaStream_t s) {
 }  // namespace gqa
 }  // namespace cake
 
+int cake::gqa_decode_plan_view(void* handle, int which, void** device_pointer_out, int* count_out) {
+  auto* h = static_cast<gqa::Handle*>(handle);
+  const gqa::Params& p = h->p;
+  int ranges = 0, grid = 0;
+  gqa::geometry(p.hkv, h->sms, &ranges, &grid);       // what a launch of this handle uses
+  switch (which) {
+    case 0: *device_pointer_out = p.items; *count_out = p.capacity; return 0;          // int4 per piece
+    case 1: *device_pointer_out = p.range_first; *count_out = ranges; return 0;
+    case 2: *device_pointer_out = p.range_count; *count_out = ranges; return 0;
+    default: return kErrBadArgument;
+  }
+}
+
 void cake::gqa_decode_launch_facts(int* threads, int* dynamic_shared_bytes) {
   *threads = cake::gqa::kWarps * 32;
   *dynamic_shared_bytes = int(cake::gqa::kSmemBytes);

@@ -11,13 +11,15 @@
 // of tiles of all sequences, so it works through one to a few sequences in turn); the two halves
 // of a range are neighbouring CTAs, so one of them reads the latent rows from L2.  The 128 heads
 // are the 128 TMEM lanes:
-//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q dims 0..319 from TENSOR memory, 320..575 and
+//   S[128 x 32 tokens]  = Q[128 x 576] . KV_tile^T      Q dims 0..383 from TENSOR memory, 384..575 and
 //                                                        the tile K-major from shared memory
 //   O[128 x 256 dims]  += P[128 x 32] . V[32 x 256]     P from tensor memory, V = the same tile read
 //                                                        MN-major (no transposed copy is made)
-// Tensor memory holds O (256 columns), S (32), two P buffers (32 each, so that the softmax of tile
-// i+1 need not wait for PV(i)) and as much of Q as fits beside them (160 columns = 320 of a row's
-// 576 bf16); the rest of Q (64 KiB) stays in shared memory.  All of Q in
+// Tensor memory holds O (256 columns), two S/P buffers of 32 columns (a tile's logits, which the softmax
+// warps overwrite in place with the tile's weights, so that the softmax of tile i+1 need not wait for
+// PV(i)) and as much of Q as fits beside them (192 columns = 384 of a row's 576 bf16: a product step
+// whose A operand comes from shared memory costs four times one that takes it from tensor memory);
+// the rest of Q (48 KiB) stays in shared memory.  All of Q in
 // shared memory would take 147 KiB, leave room for two ring stages only, and be re-read by every
 // QK (1152 clocks of shared-memory bandwidth per tile); all of Q in tensor memory leaves O only
 // 128 columns, i.e. four CTAs per range that each repeat the QK product AND the softmax.  With the
@@ -43,11 +45,11 @@ constexpr int kRowChunks = kRow / 8;                       // 72 16-byte chunks 
 constexpr int kHeads = 128;                                // query heads per CTA = TMEM lanes
 constexpr int kDimsPerCta = 256;                           // output dims per CTA (half of ckv)
 constexpr int kDimSplit = kCkv / kDimsPerCta;              // CTAs that share a (head block, tile range)
-constexpr int kQTmemSlabs = 5;                             // Q dims 0..319 live in tensor memory,
-constexpr int kQSmemSlabs = kSlabs - kQTmemSlabs;          //   dims 320..575 (four slabs) in shared memory
-constexpr int kQTmemCols = kQTmemSlabs * 32;               // 160 columns, two bf16 per column
+constexpr int kQTmemSlabs = 6;                             // Q dims 0..383 live in tensor memory,
+constexpr int kQSmemSlabs = kSlabs - kQTmemSlabs;          //   dims 384..575 (three slabs) in shared memory
+constexpr int kQTmemCols = kQTmemSlabs * 32;               // 192 columns, two bf16 per column
 constexpr int kQSlabBytes = kHeads * 128;                  // 16 KiB
-constexpr int kQSmemBytes = kQSmemSlabs * kQSlabBytes;     // 64 KiB
+constexpr int kQSmemBytes = kQSmemSlabs * kQSlabBytes;     // 48 KiB
 constexpr int kQStageRow = kQTmemSlabs * 128;              // 768 bytes of a Q row pass through the staging area
 constexpr int kTile = 32;                                  // tokens per tile
 constexpr int kStages = 4;                                 // ring stages
@@ -62,9 +64,10 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;                   // log2 units
 constexpr int kOutRowFloats = 36;                          // write-out: a row of 32 fp32 columns + 16 bytes of padding
 static_assert(kSoftmaxWarps * 32 * kOutRowFloats * 4 <= kKvStageBytes, "the write-out blocks must fit in ring stage 0");
-// tensor-memory columns: O fp32 (256), S fp32 (32), two P buffers of two bf16 terms each (2 x 32), Q dims 0..319
-// (160): all 512
-constexpr uint32_t kColO = 0, kColS = kColO + kDimsPerCta, kColP = kColS + kTile, kColQ = kColP + 2 * kTile, kTmemColumns = 512;
+// tensor-memory columns: O fp32 (256); two S/P buffers of 32 (the logits of a tile as fp32, overwritten in place by its
+// weights as two bf16 terms: each softmax warp owns 16 columns = its 16 tokens' logits, then 8 + 8 columns of P);
+// Q dims 0..383 (192): all 512
+constexpr uint32_t kColO = 0, kColSP = kColO + kDimsPerCta, kColQ = kColSP + 2 * kTile, kTmemColumns = 512;
 static_assert(kColQ + kQTmemCols <= kTmemColumns, "Q does not fit in tensor memory");
 
 struct Params {
@@ -92,8 +95,9 @@ struct Params {
 
 struct Shared {
   uint64_t kv_full[kStages], kv_empty[kStages];
-  uint64_t s_full, s_free, p_ready;               // one S buffer: the tensor pipe is in order
-  uint64_t pv_done[2];                            // two P buffers, so that the softmax of tile i+1 need not wait for PV(i)
+  uint64_t s_full[2], p_ready[2], pv_done[2];     // per S/P buffer (tile i uses buffer i mod 2)
+  uint64_t pair_read[4];                          // per lane quadrant: both warps of a row have read the tile's logits
+  uint64_t q_placed;                              // Q dims 0..383 are in tensor memory
   uint64_t row_sums;                              // the two softmax warps of a row exchange their sums once
   uint64_t q_moved;                               // Q has left its staging area (ring stages 1..3)
   uint32_t tmem_base;
@@ -170,6 +174,7 @@ __device__ __forceinline__ int units_per_worker(const Params& p) {
 __global__ void __launch_bounds__(1024)
 mla_plan_kernel(const Params p) {
   __shared__ int sums[32];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the decode grid may become resident now; it waits for this grid's end
   if (threadIdx.x == 0) *p.status = 0;
   int before = 0;
   for (int base = 0; base < p.batch; base += 1024) {
@@ -188,6 +193,8 @@ template <bool SPARSE>
 __global__ void __launch_bounds__(kThreads, 1)
 mla_decode_kernel(const Params p) {
   extern __shared__ uint8_t smem_raw[];
+  // launched as a programmatic dependent of the plan kernel: resident early, reads the plan after that grid has completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head_blocks = (p.heads + kHeads - 1) / kHeads;
   const int dq = blockIdx.x % kDimSplit, hb = (blockIdx.x / kDimSplit) % head_blocks, worker = blockIdx.x / (kDimSplit * head_blocks);
   const int per_worker = units_per_worker(p);
@@ -226,8 +233,9 @@ mla_decode_kernel(const Params p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sh->kv_full[s], kLoaderThreads); mbar_init(&sh->kv_empty[s], 1); }
-    mbar_init(&sh->s_full, 1); mbar_init(&sh->s_free, kSoftmaxWarps);
-    mbar_init(&sh->p_ready, kSoftmaxWarps); mbar_init(&sh->pv_done[0], 1); mbar_init(&sh->pv_done[1], 1);
+    for (int k = 0; k < 2; ++k) { mbar_init(&sh->s_full[k], 1); mbar_init(&sh->p_ready[k], kSoftmaxWarps); mbar_init(&sh->pv_done[k], 1); }
+    for (int k = 0; k < 4; ++k) mbar_init(&sh->pair_read[k], 2);
+    mbar_init(&sh->q_placed, kSoftmaxWarps);
     mbar_init(&sh->row_sums, kSoftmaxWarps);
     mbar_init(&sh->q_moved, kSoftmaxWarps);
     fence_barrier_init();
@@ -292,9 +300,9 @@ mla_decode_kernel(const Params p) {
       // S(i) = Q . tile(i)^T, Q from tensor memory: 36 steps of 16 elements, 8 columns of Q each
       auto issue_qk = [&](int i) {
         const int s = i % kStages;
+        // S/P buffer i mod 2 needs no wait: its last reader, PV(i-2), was issued before this product and the tensor
+        // pipe runs the products of one thread in order
         ok = mbar_wait(&sh->kv_full[s], (i / kStages) & 1, abort_flag, p.status, kStatusWaitSmemFull);
-        // S is free once the softmax warps have read tile i-1's logits (for i = 0: once Q is in place)
-        ok = ok && mbar_wait(&sh->s_free, i & 1, abort_flag, p.status, kStatusWaitTmemEmpty);
         if (!ok) return;
         fence_proxy_async_smem();               // the tile was written by cp.async (generic proxy), the MMA reads it through the async proxy
         tcgen05_fence_after();
@@ -307,22 +315,23 @@ mla_decode_kernel(const Params p) {
         for (int step = 0; step < kRow / 16; ++step) {
           const uint64_t b_desc = b_base + uint64_t(((step >> 2) * kKvSlabBytes + (step & 3) * 32) >> 4);
           if (step < kQTmemSlabs * 4) {         // Q dims 0..383 from tensor memory
-            umma_f16_a_tmem(tmem_base + kColS, tmem_base + kColQ + step * 8, b_desc, idesc_qk, step != 0);
+            umma_f16_a_tmem(tmem_base + kColSP + (i & 1) * kTile, tmem_base + kColQ + step * 8, b_desc, idesc_qk, step != 0);
           } else {                              // dims 384..575 from shared memory
             const uint64_t a_desc = a_base + uint64_t((((step >> 2) - kQTmemSlabs) * kQSlabBytes + (step & 3) * 32) >> 4);
-            umma_f16(tmem_base + kColS, a_desc, b_desc, idesc_qk, 1);
+            umma_f16(tmem_base + kColSP + (i & 1) * kTile, a_desc, b_desc, idesc_qk, 1);
           }
         }
-        tcgen05_commit(&sh->s_full);
+        tcgen05_commit(&sh->s_full[i & 1]);
       };
-      issue_qk(0);
+      ok = mbar_wait(&sh->q_placed, 0, abort_flag, p.status, kStatusWaitTmemEmpty);
+      if (ok) issue_qk(0);
       for (int i = 0; ok && i < tiles; ++i) {
         // QK of the next tile first: the tensor pipe works on it while the softmax of tile i runs
         if (i + 1 < tiles) issue_qk(i + 1);
         if (!ok) break;
         // O += P(i) . V(i), P as two bf16 terms
         const int s = i % kStages;
-        ok = mbar_wait(&sh->p_ready, i & 1, abort_flag, p.status, kStatusWaitFlag);
+        ok = mbar_wait(&sh->p_ready[i & 1], (i >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
         if (!ok) break;
         tcgen05_fence_after();
         // 16 tokens = two 8-row groups of 1024 bytes; the next 64 dims are one slab further
@@ -331,7 +340,7 @@ mla_decode_kernel(const Params p) {
         for (int term = 0; term < 2; ++term) {
 #pragma unroll
           for (int ks = 0; ks < kTile / 16; ++ks) {
-            const uint32_t a_tmem = tmem_base + kColP + (i & 1) * kTile + term * (kTile / 2) + ks * 8;
+            const uint32_t a_tmem = tmem_base + kColSP + (i & 1) * kTile + ks * 16 + term * 8;    // warp ks's columns
             umma_f16_a_tmem(tmem_base + kColO, a_tmem, v_base + uint64_t((ks * 2048) >> 4), idesc_pv, (i | term | ks) != 0);
           }
         }
@@ -352,10 +361,10 @@ mla_decode_kernel(const Params p) {
     constexpr int kOwnCols = kDimsPerCta / 2;       // O columns per warp group
     bool ok = true;
     {
-      // Q rows, staging area -> tensor memory: dims 0..319 = 160 columns, two elements per column;
+      // Q rows, staging area -> tensor memory: dims 0..383 = 192 columns, two elements per column;
       // group 0 stores columns 0..95, group 1 the rest.  Heads past the end are rows of zeros.
 #pragma unroll 1
-      for (int c = grp * 96; c < (grp == 0 ? 96 : kQTmemCols); c += 32) {       // 32 columns = 8 x 16 bytes per store
+      for (int c = grp * (kQTmemCols / 2); c < (grp + 1) * (kQTmemCols / 2); c += 32) {       // 32 columns = 8 x 16 bytes per store
         uint32_t w[32];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -370,19 +379,19 @@ mla_decode_kernel(const Params p) {
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->s_free);      // phase 0 of s_free: Q is in place
+      if (lane == 0) mbar_arrive(&sh->q_placed);
     }
     float m_ref = -INFINITY, l = 0.f;               // l: this group's share of the row sum
     for (int i = 0; ok && i < tiles; ++i) {
-      ok = mbar_wait(&sh->s_full, i & 1, abort_flag, p.status, kStatusWaitTmemFull);
+      ok = mbar_wait(&sh->s_full[i & 1], (i >> 1) & 1, abort_flag, p.status, kStatusWaitTmemFull);
       if (!ok) break;
       tcgen05_fence_after();
       float sc[kTile];
-      tmem_ld_32x32b_x32(lane_base + kColS, sc);
+      tmem_ld_32x32b_x32(lane_base + kColSP + (i & 1) * kTile, sc);
       tcgen05_wait_ld();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->s_free);      // phase i+1: S may be overwritten by QK(i+1)
+      if (lane == 0) mbar_arrive(&sh->pair_read[quad]);    // this warp has the logits: its partner may write P over its own half
       // The softmax of a tile sits between QK(i) and PV(i): four-way partial maxima and sums keep
       // its dependent chains short.
       const int tok0 = begin + i * kTile;
@@ -449,12 +458,15 @@ mla_decode_kernel(const Params p) {
         split_bf16x2(p0, p1, hi[c >> 1], lo[c >> 1]);
       }
       l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
-      tmem_st_32x32b_x8(lane_base + kColP + (i & 1) * kTile + grp * (kTile / 4), hi);
-      tmem_st_32x32b_x8(lane_base + kColP + (i & 1) * kTile + kTile / 2 + grp * (kTile / 4), lo);
+      // P goes over the logits of this warp's own 16 tokens, once the row's other warp has read them too
+      ok = mbar_wait(&sh->pair_read[quad], i & 1, abort_flag, p.status, kStatusWaitFlag);
+      if (!ok) break;
+      tmem_st_32x32b_x8(lane_base + kColSP + (i & 1) * kTile + grp * (kTile / 2), hi);
+      tmem_st_32x32b_x8(lane_base + kColSP + (i & 1) * kTile + grp * (kTile / 2) + kTile / 4, lo);
       tcgen05_wait_st();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->p_ready);
+      if (lane == 0) mbar_arrive(&sh->p_ready[i & 1]);
     }
     // the row sum is the two groups' sums; exchanged once through shared memory
     if (ok) {
@@ -560,6 +572,15 @@ inline size_t slots_for(const cake_b200_mla_decode_config& c) { return size_t(kM
 }  // namespace mla
 }  // namespace cake
 
+int cake::mla_decode_plan_view(void* handle, int which, void** device_pointer_out, int* count_out) {
+  auto* h = static_cast<mla::Handle*>(handle);
+  switch (which) {
+    case 0: *device_pointer_out = h->p.tile_prefix; *count_out = h->p.batch + 1; return 0;
+    case 1: *device_pointer_out = nullptr; *count_out = h->p.workers; return 0;         // ranges the unit list is cut into
+    default: return kErrBadArgument;
+  }
+}
+
 void cake::mla_decode_launch_facts(int* threads, int* dynamic_shared_bytes) {
   *threads = cake::mla::kThreads;
   *dynamic_shared_bytes = int(cake::mla::kSmemBytes);
@@ -644,23 +665,26 @@ extern "C" int cake_b200_mla_decode_launch(void* handle, void* cuda_stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(cuda_stream);
   const int head_blocks = (p.heads + mla::kHeads - 1) / mla::kHeads;
   mla::mla_plan_kernel<<<1, 1024, 0, s>>>(p);
-  if (p.sparse_indices) mla::mla_decode_kernel<true><<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
-  else mla::mla_decode_kernel<false><<<p.workers * mla::kDimSplit * head_blocks, mla::kThreads, mla::kSmemBytes, s>>>(p);
-  {
-    // The reduce grid is a programmatic dependent of the decode grid, which takes its launch latency
-    // off the end of the operator.
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(p.heads, p.batch);
-    config.blockDim = dim3(128);
-    config.stream = s;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&config, mla::mla_reduce_kernel, p);
-    if (err != cudaSuccess) return int(err);
-  }
+  // The decode grid is a programmatic dependent of the plan grid and the reduce grid one of the decode grid: each
+  // is resident (and past its launch latency) when the grid before it ends.
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config = {};
+  config.stream = s;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  config.gridDim = dim3(p.workers * mla::kDimSplit * head_blocks);
+  config.blockDim = dim3(mla::kThreads);
+  config.dynamicSmemBytes = mla::kSmemBytes;
+  cudaError_t err = p.sparse_indices ? cudaLaunchKernelEx(&config, mla::mla_decode_kernel<true>, p)
+                                     : cudaLaunchKernelEx(&config, mla::mla_decode_kernel<false>, p);
+  if (err != cudaSuccess) return int(err);
+  config.gridDim = dim3(p.heads, p.batch);
+  config.blockDim = dim3(128);
+  config.dynamicSmemBytes = 0;
+  err = cudaLaunchKernelEx(&config, mla::mla_reduce_kernel, p);
+  if (err != cudaSuccess) return int(err);
   return int(cudaGetLastError());
 }
 

@@ -268,26 +268,29 @@ struct PushScratch {       // ints in the rank's own (non-symmetric) scratch, af
   int* slot_of;            // [T, world]
 };
 
-// One warp per destination rank: slots of the tokens that rank needs, in token order; the row count; and the epoch.
-__global__ void __launch_bounds__(32)
+// One CTA of 1024 threads per destination rank: slots of the tokens that rank needs, in token order (a block-wide
+// exclusive scan per 1024 tokens); the row count; and the epoch.
+__global__ void __launch_bounds__(1024)
 push_plan_kernel(const int* __restrict__ expert_ids, PushScratch sc, int tokens, int top_k, int world, int experts_per_rank) {
-  const int r = blockIdx.x, lane = threadIdx.x;
-  const uint32_t below = (1u << lane) - 1u;
+  __shared__ int warp_sums[32];
+  const int r = blockIdx.x;
   int cursor = 0;
-  for (int base = 0; base < tokens; base += 32) {
-    const int t = base + lane;
-    bool need = false;
+  for (int base = 0; base < tokens; base += 1024) {
+    const int t = base + threadIdx.x;
+    int need = 0;
     if (t < tokens) {
-      for (int k = 0; k < top_k; ++k) {
-        const int e = expert_ids[size_t(t) * top_k + k];
-        need |= (e >= 0 && e / experts_per_rank == r);
+      const int* row = expert_ids + size_t(t) * top_k;
+      for (int k = 0; k < top_k; k += 2) {                 // top_k is even (checked at create): 8-byte loads
+        const int2 e = *reinterpret_cast<const int2*>(row + k);
+        need |= (e.x >= 0 && e.x / experts_per_rank == r) || (e.y >= 0 && e.y / experts_per_rank == r);
       }
     }
-    const uint32_t mask = __ballot_sync(0xffffffffu, need);
-    if (t < tokens) sc.slot_of[size_t(t) * world + r] = need ? cursor + __popc(mask & below) : -1;
-    cursor += __popc(mask);
+    int total;
+    const int before = cta1024_exclusive_scan(need, warp_sums, total);
+    if (t < tokens) sc.slot_of[size_t(t) * world + r] = need ? cursor + before : -1;
+    cursor += total;
   }
-  if (lane == 0) {
+  if (threadIdx.x == 0) {
     sc.send_count[r] = cursor;
     if (r == 0) *sc.epoch = *sc.epoch + 1;
   }
@@ -554,7 +557,7 @@ extern "C" int cake_b200_ep_push_launch_stage(void* handle, int stage, void* cud
   auto* own = static_cast<const uint8_t*>(h->b[5]);
   switch (stage) {
     case 0: {  // plan + dispatch: this rank's rows go into their owners' receive blocks
-      ep::push_plan_kernel<<<c.world, 32, 0, s>>>(ids, h->sc, tokens, c.top_k, c.world, c.experts / c.world);
+      ep::push_plan_kernel<<<c.world, 1024, 0, s>>>(ids, h->sc, tokens, c.top_k, c.world, c.experts / c.world);
       const int blocks = tokens > 0 ? (tokens * c.world + 7) / 8 : 1;
       ep::push_dispatch_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(hidden, scale, ids, weights, h->sc, peers, tokens, c.top_k,
                                                                            c.world, c.rank, cap, c.hidden);

@@ -15,6 +15,14 @@ extern "C" int cake_b200_launch_facts(const char* kernel, int* threads_per_cta, 
   return 0;
 }
 
+extern "C" int cake_b200_decode_plan_view(const char* kind, void* handle, int which, void** device_pointer_out, int* count_out) {
+  if (!kind || !handle || !device_pointer_out || !count_out) return cake::kErrBadArgument;
+  const std::string name(kind);
+  if (name == "gqa_decode") return cake::gqa_decode_plan_view(handle, which, device_pointer_out, count_out);
+  if (name == "mla_decode") return cake::mla_decode_plan_view(handle, which, device_pointer_out, count_out);
+  return cake::kErrBadArgument;
+}
+
 extern "C" int cake_b200_test_hooks(int wait_budget_kiloclocks, int skip_load) {
   if (wait_budget_kiloclocks < 0) return cake::kErrBadArgument;
   cake::test_hooks().budget_kiloclocks = wait_budget_kiloclocks;
