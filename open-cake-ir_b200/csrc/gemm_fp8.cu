@@ -8,7 +8,7 @@ namespace {
 
 struct DenseHandle {
   int device;
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_a_tail, map_b;
   gemm::Params params;
   int grid;
   int* status;
@@ -40,6 +40,7 @@ extern "C" int cake_b200_block_scaled_gemm_create(void** buffers, const cake_b20
   if (!h) return int(cudaErrorMemoryAllocation);
   h->device = device;
   int rc = make_tensor_map_u8_sw128(&h->map_a, buffers[0], uint64_t(m), uint64_t(k), gemm::kBM);
+  if (!rc) rc = make_tensor_map_u8_sw128(&h->map_a_tail, buffers[0], uint64_t(m), uint64_t(k), gemm::kTailRows);
   if (!rc) rc = make_tensor_map_u8_sw128(&h->map_b, buffers[2], uint64_t(n), uint64_t(k), gemm::kBN);
   if (!rc) rc = int(cudaFuncSetAttribute(gemm::gemm_fp8_kernel<gemm::kDense>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm::kSmemBytes)));
@@ -78,7 +79,7 @@ extern "C" int cake_b200_block_scaled_gemm_launch(void* handle, void* cuda_strea
   gemm::Params p = h->params;
   p.wait_kiloclocks = test_hooks().budget_kiloclocks;
   p.skip_load = test_hooks().skip_load;
-  gemm::gemm_fp8_kernel<gemm::kDense><<<h->grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(h->map_a, h->map_b, p);
+  gemm::gemm_fp8_kernel<gemm::kDense><<<h->grid, gemm::kThreads, gemm::kSmemBytes, stream>>>(h->map_a, h->map_a_tail, h->map_b, p);
   return int(cudaGetLastError());
 }
 

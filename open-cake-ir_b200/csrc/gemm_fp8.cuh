@@ -38,6 +38,7 @@ constexpr int kTmemColumns = kTmemStages * kBN;   // 512 = all of an SM's tensor
 constexpr int kBytesA = kBM * kBK;                // 16 KiB
 constexpr int kBytesB = kBN * kBK;                // 32 KiB
 constexpr int kStageBytes = kBytesA + kBytesB;
+constexpr int kTailRows = 32;                    // box rows of the small A map
 constexpr int kControlWarps = 4;                  // one warpgroup: warp 0 TMA, warp 1 MMA, warps 2-3 idle
 constexpr int kEpilogueWarps = 8;                 // two warpgroups: 2 column groups x 4 TMEM lane quadrants
 constexpr int kThreads = (kControlWarps + kEpilogueWarps) * 32;
@@ -122,8 +123,8 @@ __device__ __forceinline__ bool locate(const Shared* sh, const Params& p, int n_
 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const Params p) {
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_tail,
+                const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Shared* sh = reinterpret_cast<Shared*>(tiles + kStages * kStageBytes);
@@ -176,6 +177,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------ TMA producer --------------------------------------
     if (elect_one()) {
       tma_prefetch_descriptor(&map_a);
+      tma_prefetch_descriptor(&map_a_tail);
       tma_prefetch_descriptor(&map_b);
       const uint64_t keep = l2_policy_evict_last();    // activations: re-read by every n tile
       // Work items.  With a queue, this thread draws them (the first is the CTA's index, every later
@@ -199,6 +201,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         if (!valid) break;
         const int b_row0 = item.group * p.b_rows_per_group;
+        // A tile of at most kTailRows valid rows (the second tile of a group a little over 128 rows) brings in those
+        // rows only, through a map with a smaller box: such a tile streams its weights from L2 at what one SM can
+        // draw, so every byte not fetched shortens it.  Rows of the stage beyond them keep what an earlier tile left
+        // there; their products land in accumulator rows that no one reads.
+        const bool tail = item.rows_valid <= kTailRows;
+        const uint32_t stage_tx = tail ? uint32_t(kTailRows * kBK + kBytesB) : uint32_t(kStageBytes);
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           ok = mbar_wait(&sh->empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status, kStatusWaitSmemEmpty);
@@ -208,8 +216,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           uint8_t* b_dst = a_dst + kBytesA;
           int a_col = kb, b_col = kb;
           if (p.interleave_hi_lo) { a_col = (kb & 1) * (p.k_blocks >> 1) + (kb >> 1); b_col = kb >> 1; }
-          mbar_arrive_expect_tx(&sh->full[s], kStageBytes);
-          tma_load_2d_hint(a_dst, &map_a, a_col * kBK, item.row0, &sh->full[s], keep);
+          mbar_arrive_expect_tx(&sh->full[s], stage_tx);
+          tma_load_2d_hint(a_dst, tail ? &map_a_tail : &map_a, a_col * kBK, item.row0, &sh->full[s], keep);
           if (MODE == kGateUp) {
             // gate/up: 128 rows of the first half (x1) and the matching 128 rows of the second half (x2)
             tma_load_2d(b_dst, &map_b, b_col * kBK, b_row0 + item.n_tile * 128, &sh->full[s]);

@@ -379,7 +379,7 @@ struct MoeHandle {
   const int* local_offset; const float* factor;
   __nv_bfloat16* output;
   int* expert_ids; float* route_weights;       // in the workspace, or the caller's when routing is external
-  CUtensorMap map_a1, map_b1, map_a2, map_b2;
+  CUtensorMap map_a1, map_a1_tail, map_b1, map_a2, map_a2_tail, map_b2;
   gemm::Params p1, p2;
   int grid;
 };
@@ -511,6 +511,8 @@ extern "C" int cake_b200_moe_create(void** buffers, const cake_b200_moe_config* 
   }
   const int inter = c.intermediate, hidden = c.hidden;
   int rc = make_tensor_map_u8_sw128(&h->map_a1, h->ws + l.x_perm, uint64_t(l.capacity), uint64_t(hidden), gemm::kBM);
+  if (!rc) rc = make_tensor_map_u8_sw128(&h->map_a1_tail, h->ws + l.x_perm, uint64_t(l.capacity), uint64_t(hidden), gemm::kTailRows);
+  if (!rc) rc = make_tensor_map_u8_sw128(&h->map_a2_tail, h->ws + l.act, uint64_t(l.capacity), uint64_t(inter) * l.terms, gemm::kTailRows);
   if (!rc) rc = make_tensor_map_u8_sw128(&h->map_b1, buffers[4], uint64_t(c.local_experts) * 2 * inter, uint64_t(hidden), 128);
   if (!rc) rc = make_tensor_map_u8_sw128(&h->map_a2, h->ws + l.act, uint64_t(l.capacity), uint64_t(inter) * l.terms, gemm::kBM);
   if (!rc) rc = make_tensor_map_u8_sw128(&h->map_b2, buffers[6], uint64_t(c.local_experts) * hidden, uint64_t(inter), gemm::kBN);
@@ -583,14 +585,14 @@ static int moe_launch_stage(cake::moe::MoeHandle* h, int stage, cudaStream_t s) 
       if (h->p1.queue) CAKE_CUDA_OK(cudaMemsetAsync(h->p1.queue, 0, sizeof(int), s));     // the work-item counter starts at 0
       gemm::Params p = h->p1;
       p.wait_kiloclocks = test_hooks().budget_kiloclocks;
-      gemm::gemm_fp8_kernel<gemm::kGateUp><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a1, h->map_b1, p);
+      gemm::gemm_fp8_kernel<gemm::kGateUp><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a1, h->map_a1_tail, h->map_b1, p);
       break;
     }
     case 2: {
       if (h->p2.queue) CAKE_CUDA_OK(cudaMemsetAsync(h->p2.queue, 0, sizeof(int), s));
       gemm::Params p = h->p2;
       p.wait_kiloclocks = test_hooks().budget_kiloclocks;
-      gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_b2, p);
+      gemm::gemm_fp8_kernel<gemm::kDown><<<h->grid, gemm::kThreads, gemm::kSmemBytes, s>>>(h->map_a2, h->map_a2_tail, h->map_b2, p);
       break;
     }
     case 3:
