@@ -240,10 +240,9 @@ def pipelined_e2e(make_set, dev, out):
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE gemm_fp8_kernel<kGateUp> launch, from an ncu capture of
 # `bench.py --profile-case moe` (1024 tokens over 64 experts: 128 tokens per expert as at full size), and the
 # algorithmic bytes of that case.  Every expert's weights are read once, so traffic grows with the number of
-# experts and the full layer's figure is this ratio times its algorithmic bytes.  (1.23 x algorithmic: the second,
-# nearly empty row tile of an expert with more than 128 tokens runs ahead of the full tile on the neighbouring SM,
-# and part of the weights it fetched have left L2 again when the full tile asks for them.)
-NCU_GEMM1_CASE = {"traffic_bytes": 2.402e9, "algorithmic_bytes": 64 * 2 * 2048 * 7168 + 8192 * (7168 + 2048)}
+# experts and the full layer's figure is this ratio times its algorithmic bytes (1.006 x algorithmic: every weight
+# byte is read from DRAM once; the second row tile of an expert finds it in L2).
+NCU_GEMM1_CASE = {"traffic_bytes": 1.966e9, "algorithmic_bytes": 64 * 2 * 2048 * 7168 + 8192 * (7168 + 2048)}
 
 
 def stage_times(op, steps):

@@ -535,7 +535,8 @@ extern "C" int cake_b200_moe_create(void** buffers, const cake_b200_moe_config* 
   p1.out_scale = reinterpret_cast<float*>(h->ws + l.act_scale);
   p1.split_act = l.terms == 2;
   p1.status = status;
-  p1.queue = nullptr;                    // GEMM1: items go round the CTAs in turn (measured: drawing them from a counter is 1.5 % slower here)
+  p1.queue = status + 9;                 // GEMM1: items drawn from a counter too: the two row tiles of an expert then start together on two SMs
+                                         // and the second reads the weights from L2 (DRAM reads 1.12 -> 1.00 x algorithmic, 2 % less time)
   gemm::Params& p2 = h->p2;
   p2 = gemm::Params{};
   p2.n = hidden;
