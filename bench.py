@@ -430,12 +430,32 @@ def moe_parallel(steps, warmup, world, rank, cohorts, exchange):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
             exchange = "nccl"
-    layer_class = ep.PushExpertParallelMoe if exchange == "push" else ep.NativeExpertParallelMoe
-    layer = layer_class(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
-                        dev["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"], routing="softmax")
-    parity = ep_parity(world, rank, layer, dev, layer_class)
-    verdict = torch.tensor([1 if (rank != 0 or parity.get("ok")) else 0], device="cuda")
+
+    def build(kind):
+        cls = ep.PushExpertParallelMoe if kind == "push" else ep.NativeExpertParallelMoe
+        made = cls(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                   dev["hidden_states_scale"], experts=SHAPE["experts"], top_k=SHAPE["top_k"], routing="softmax")
+        checked = ep_parity(world, rank, made, dev, cls)
+        fine = (rank != 0 or bool(checked.get("ok"))) and not (kind == "push" and made.status())
+        return cls, made, checked, fine
+
+    try:
+        layer_class, layer, parity, fine = build(exchange)
+    except Exception as error:                          # noqa: BLE001 - reported, then the other exchange is tried
+        print(f"bench: the {exchange} exchange failed on rank {rank}: {error!r}", file=sys.stderr, flush=True)
+        layer_class = layer = None
+        parity, fine = {"ok": False, "error": repr(error)}, False
+    verdict = torch.tensor([1 if fine else 0], device="cuda")
     dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    if int(verdict.item()) == 0 and exchange == "push":
+        # the push exchange did not hold on this box (a wait ran out, or parity failed): the NCCL form takes over
+        if rank == 0:
+            print(f"bench: push exchange rejected ({parity}); using the NCCL exchange", file=sys.stderr, flush=True)
+        exchange = "nccl"
+        layer = None
+        layer_class, layer, parity, fine = build(exchange)
+        verdict = torch.tensor([1 if fine else 0], device="cuda")
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
     if int(verdict.item()) == 0:
         if rank == 0:
             print(json.dumps({"metric": "fp8_moe_tflops", "ep_parity": parity, "error": "expert-parallel output differs from the oracle"}), flush=True)
