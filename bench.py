@@ -379,7 +379,9 @@ def ep_parity(world, rank, layer, dev, layer_class):
                       rel_frobenius=compare.rel_frobenius(got, want), max_abs=float(err), mismatches=int(bad), ok=bool(ok))
     small_layer.close()
     del small_layer, sd
-    # (b) the bench shape
+    # (b) the bench shape (the ranks meet first: rank 0 has just spent seconds in the oracle above)
+    import torch.distributed as dist
+    dist.barrier()
     out_local = layer.forward()
     torch.cuda.synchronize()
     if rank == 0:

@@ -345,13 +345,19 @@ push_dispatch_kernel(const uint8_t* __restrict__ hidden_states, const float* __r
 }
 
 // Waits (bounded) until every source's flag has reached this step's epoch; returns the counts in shared memory.
+// A wait for another RANK covers whatever keeps that rank's host from launching its step on time (a collective a
+// few lines earlier, a pause of its process), not just kernel latencies, so its budget is longer than that of the
+// waits inside one kernel: about ten seconds of clocks instead of one.  It is still a bound: a rank that never
+// arrives makes this rank report through the status word and go on.
+constexpr long long kPeerWaitClockBudget = 20000000000LL;
+
 __device__ __forceinline__ void wait_for_sources(const int* flags, const int* counts, int world, int epoch, int* status,
                                                  int* cnt /* shared [kMaxWorld] */) {
   if (threadIdx.x < world) {
     const long long start = clock64();
     bool ok = true;
     while (ld_acquire_sys(flags + threadIdx.x) < epoch) {
-      if (clock64() - start > kWaitClockBudget) { ok = false; if (status) atomicCAS(status, 0, kStatusWaitFlag); break; }
+      if (clock64() - start > kPeerWaitClockBudget) { ok = false; if (status) atomicCAS(status, 0, kStatusWaitFlag); break; }
       __nanosleep(64);
     }
     cnt[threadIdx.x] = ok && counts ? counts[threadIdx.x] : 0;

@@ -307,13 +307,21 @@ class PushExpertParallelMoe:
 
     def __init__(self, weights: dict, routing_logits, routing_bias, hidden_states, hidden_states_scale, *,
                  experts: int, top_k: int = 8, routing: str = "softmax", n_group: int = 8, topk_group: int = 4,
-                 act_mode: str = "fp8", group=None):
+                 act_mode: str = "fp8", group=None, virtual=None):
+        """``virtual = (rank, world, buffers)`` makes this object one of ``world`` ranks that all live in this
+        process on one GPU (``buffers``: one uint8 tensor of ``push_symmetric_bytes`` + 256 bytes per rank, zero-filled,
+        shared by all of them), for tests that have fewer GPUs than ranks: the caller then runs the parts of a step
+        (``_parts()``) in lock step, each part on every rank before the next, so that no kernel ever waits for a
+        kernel that has not been launched."""
         import ctypes
 
         from . import _lib, ops
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if virtual is not None:
+            self.rank, self.world = int(virtual[0]), int(virtual[1])
+        else:
+            self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         dev = hidden_states.device
         self.device = dev
         tokens, hidden = hidden_states.shape
@@ -327,7 +335,10 @@ class PushExpertParallelMoe:
             raise ValueError("unsupported expert-parallel configuration (hidden must be a multiple of 512 and top_k even)")
         i32, f32 = torch.int32, torch.float32
         with torch.cuda.device(dev):
-            if self.world > 1:
+            if virtual is not None:
+                self.symmetric = virtual[2][self.rank]
+                bases = [(b.data_ptr() + 255) // 256 * 256 for b in virtual[2]]
+            elif self.world > 1:
                 import torch.distributed._symmetric_memory as symm
                 self.symmetric = symm.empty(sym_bytes, dtype=torch.uint8, device=dev)
                 self.symmetric.zero_()
@@ -368,7 +379,7 @@ class PushExpertParallelMoe:
         if code:
             raise _lib.CakeError("cake_b200_ep_push_create", code)
         self._lib = _lib
-        if self.world > 1:
+        if self.world > 1 and virtual is None:
             dist.barrier(group)            # every rank's buffers are zeroed and mapped before anyone pushes
         # kernels of this library launched per step: routing 1, exchange 6, rank-local layer stages 0..2: 6
         self.launches_per_step = 13
@@ -395,6 +406,15 @@ class PushExpertParallelMoe:
     capture = NativeExpertParallelMoe.capture
     forward = NativeExpertParallelMoe.forward
     stage_times = NativeExpertParallelMoe.stage_times
+
+    @staticmethod
+    def symmetric_bytes(tokens: int, hidden: int, top_k: int, world: int, experts: int) -> int:
+        """Bytes of one rank's symmetric buffer (``cake_b200_ep_push_symmetric_bytes``)."""
+        import ctypes
+
+        from . import _lib
+        cfg = _lib.EpPushConfig(tokens, tokens, hidden, top_k, world, experts, 0)
+        return int(_lib.library().cake_b200_ep_push_symmetric_bytes(ctypes.byref(cfg)))
 
     def status(self) -> int:
         """0, or 5 when a wait for another rank's rows ran out (synchronises the stream)."""

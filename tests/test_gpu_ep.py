@@ -105,3 +105,46 @@ def test_single_rank_push_exchange_is_the_identity():
     got = layer.forward()
     torch.cuda.synchronize()
     assert layer.status() == 0 and torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def _virtual_ranks_step(layers):
+    """One step of `layers` (the ranks of one expert-parallel group, all in this process on one GPU): every part of
+    the step on every rank before the next part, so that each wait finds its flags already set."""
+    parts = [layer._parts() for layer in layers]
+    for i in range(len(parts[0])):
+        for rank_parts in parts:
+            rank_parts[i]()
+    torch.cuda.synchronize()
+    return torch.cat([layer.output for layer in layers])
+
+
+@pytest.mark.parametrize("world,tokens,shape", [
+    (4, 512, dict(hidden=1024, inter=512, experts=32)),
+    (4, 4096, dict(hidden=7168, inter=512, experts=256)),
+    (8, 4096, dict(hidden=7168, inter=512, experts=256)),
+    (8, 1000 // 8 * 8, dict(hidden=1024, inter=512, experts=64)),
+], ids=["4-ranks-small", "4-ranks-serving-rows", "8-ranks-serving-rows", "8-ranks-ragged"])
+def test_push_exchange_with_virtual_ranks_on_one_gpu(world, tokens, shape):
+    """The push exchange at 4 and 8 ranks without 4 or 8 GPUs: all ranks live on one GPU with ordinary buffers in
+    place of the symmetric ones and run the parts of a step in lock step.  The result must be the single-GPU layer's
+    over all tokens and experts, at the tolerance of bf16 partial rows, over several steps."""
+    t_local, e_local = tokens // world, shape["experts"] // world
+    sym = ep.PushExpertParallelMoe.symmetric_bytes(t_local, shape["hidden"], 8, world, shape["experts"])
+    buffers = [torch.zeros(sym + 256, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    layers = []
+    for rank in range(world):
+        dev = cake.workloads.moe_inputs(tokens=t_local, **shape, local_experts=e_local, local_offset=rank * e_local,
+                                        routing="softmax", device="cuda", gen_device="cuda",
+                                        first_token=rank * t_local, total_tokens=tokens)
+        layers.append(ep.PushExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                                               dev["hidden_states_scale"], experts=shape["experts"], routing="softmax",
+                                               virtual=(rank, world, buffers)))
+    whole = cake.workloads.moe_inputs(tokens=tokens, **shape, local_experts=shape["experts"], local_offset=0,
+                                      routing="softmax", device="cuda", gen_device="cuda")
+    want = cake.fp8_moe(whole, experts=shape["experts"], routing="softmax", act_mode="fp8")
+    for _ in range(3):
+        got = _virtual_ranks_step(layers)
+        assert all(layer.status() == 0 for layer in layers)
+        assert compare.rel_frobenius(got.cpu(), want.cpu()) <= 1e-2
+        assert compare.compare(got.cpu(), want.cpu(), atol=2e-2, rtol=2e-2)[0]
+    assert sum(layer.rows_sent() for layer in layers) >= tokens
