@@ -416,27 +416,39 @@ __global__ void __launch_bounds__(256)
 push_return_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ inv_perm, PushScratch sc,
                    const unsigned long long* __restrict__ peer_bases, int world, int me, int capacity, int hidden, int top_k) {
   __shared__ int rows_of[32];
+  __shared__ int valid_rows;
   const int c = blockIdx.x;
   const int total = *sc.recv_total;
   if (c < total) {
-    if (threadIdx.x < top_k) rows_of[threadIdx.x] = inv_perm[size_t(c) * top_k + threadIdx.x];
+    if (threadIdx.x < 32) {              // the row's local contributions, compacted, still in slot order
+      const int row = threadIdx.x < top_k ? inv_perm[size_t(c) * top_k + threadIdx.x] : -1;
+      const uint32_t have = __ballot_sync(0xffffffffu, row >= 0);
+      if (row >= 0) rows_of[__popc(have & ((1u << threadIdx.x) - 1u))] = row;
+      if (threadIdx.x == 0) valid_rows = __popc(have);
+    }
     __syncthreads();
+    const int n = valid_rows;
     const int src = sc.row_src[c], slot = sc.row_slot[c];
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(peer_bases[src]) +
                                                           returned_offset(world, capacity, hidden, top_k)) +
                          (size_t(me) * capacity + slot) * hidden;
     for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int s = 0; s < top_k; ++s) {
-        const int row = rows_of[s];
-        if (row < 0) continue;
-        const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y + size_t(row) * hidden + col));
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      for (int s0 = 0; s0 < n; s0 += 4) {          // four loads in flight, added in slot order
+        uint4 raw[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h[i]);
-          acc[2 * i] += f.x;
-          acc[2 * i + 1] += f.y;
+        for (int j = 0; j < 4; ++j)
+          raw[j] = s0 + j < n ? __ldcs(reinterpret_cast<const uint4*>(y + size_t(rows_of[s0 + j]) * hidden + col)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (s0 + j >= n) break;
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
+          }
         }
       }
       uint4 o;

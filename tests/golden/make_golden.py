@@ -97,4 +97,6 @@ def main(reference: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(f"usage: python {Path(__file__).name} <path of a checkout of the reference>")
+    main(sys.argv[1])
