@@ -115,3 +115,24 @@ def test_ep_rows_must_stay_sixteen_byte_aligned():
     assert width(1024, 8) == 1024 + 32 + 64
     assert width(1024, 1) == 0 and width(1024, 7) == 0
     assert width(640, 8) == 0
+
+
+def test_push_exchange_sizes_and_refusals():
+    """The symmetric buffer of the push exchange is flags (1 KiB) | one packed row per (source rank, slot) | one bf16
+    partial row per (source rank, slot); a rank outside the world, a world above 64 ranks and a row width that is not
+    a multiple of 16 bytes are refused by returning 0."""
+    import ctypes
+    lib = cake._lib.library()
+
+    def sizes(tokens, hidden, top_k, world, experts, rank):
+        cfg = cake._lib.EpPushConfig(tokens, tokens, hidden, top_k, world, experts, rank)
+        return (int(lib.cake_b200_ep_push_symmetric_bytes(ctypes.byref(cfg))), int(lib.cake_b200_ep_push_scratch_bytes(ctypes.byref(cfg))))
+
+    sym, scratch = sizes(512, 7168, 8, 8, 256, 3)
+    row = 7168 + 4 * 56 + 8 * 8
+    assert sym == 1024 + 8 * 512 * row + 8 * 512 * 7168 * 2 and scratch > 0 and scratch % 256 == 0
+    assert sizes(512, 7168, 8, 8, 256, 8) == (0, 0)          # rank outside the world
+    assert sizes(512, 7168, 8, 128, 256, 0) == (0, 0)        # more ranks than the flag block holds
+    assert sizes(512, 7168, 7, 8, 256, 0) == (0, 0)          # odd top_k: rows would lose their 16-byte alignment
+    from open_cake_ir_b200 import ep
+    assert ep.PushExpertParallelMoe.symmetric_bytes(512, 7168, 8, 8, 256) == sym
