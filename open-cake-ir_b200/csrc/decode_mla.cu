@@ -114,6 +114,13 @@ __device__ __forceinline__ int seq_len(const Params& p, int b) {
   const int pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
   return pages <= 0 ? 0 : (pages - 1) * p.page_size + p.kv_last_page_len[b];
 }
+// 2^x by the special-function unit alone (relative error 2^-22; results below 2^-126 become 0, which is what a
+// softmax weight that small is worth).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;      // 0 source bytes = zero fill
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -358,6 +365,8 @@ mla_decode_kernel(const Params p) {
     const int r = quad * 32 + lane;                 // head row of this thread
     const uint32_t lane_base = tmem_base + (uint32_t(quad * 32) << 16);
     const float scale2 = __ldg(p.sm_scale) * kLog2e;
+    const bool scale_positive = scale2 > 0.f;      // the contract's scales are; any other is applied to the logits first
+    const float pre = scale_positive ? 1.f : scale2, post = scale_positive ? scale2 : 1.f;
     constexpr int kOwnCols = kDimsPerCta / 2;       // O columns per warp group
     bool ok = true;
     {
@@ -401,23 +410,25 @@ mla_decode_kernel(const Params p) {
         const uint32_t present = __ballot_sync(0xffffffffu, tok < end && __ldg(p.sparse_indices + page_base + tok) >= 0);
 #pragma unroll
         for (int c = 0; c < kTile; ++c) {
-          sc[c] = ((present >> c) & 1u) ? sc[c] * scale2 : -INFINITY;
+          sc[c] = ((present >> c) & 1u) ? sc[c] * pre : -INFINITY;
           t4[c & 3] = fmaxf(t4[c & 3], sc[c]);
         }
       } else if (tok0 + kTile <= end) {              // all but a chunk's last tile
 #pragma unroll
         for (int c = 0; c < kTile; ++c) {
-          sc[c] *= scale2;
+          if (!scale_positive) sc[c] *= pre;
           t4[c & 3] = fmaxf(t4[c & 3], sc[c]);
         }
       } else {
 #pragma unroll
         for (int c = 0; c < kTile; ++c) {
-          sc[c] = tok0 + c < end ? sc[c] * scale2 : -INFINITY;
+          sc[c] = tok0 + c < end ? sc[c] * pre : -INFINITY;
           t4[c & 3] = fmaxf(t4[c & 3], sc[c]);
         }
       }
-      const float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
+      // the maximum of the scaled logits; with a positive scale the logits themselves stay unscaled and the scale
+      // rides in the multiply-add in front of the exponential
+      const float tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])) * post;
       if (i >= 2) {              // this tile's P buffer is free once PV(i-2), which read it, has completed
         ok = mbar_wait(&sh->pv_done[i & 1], ((i - 2) >> 1) & 1, abort_flag, p.status, kStatusWaitFlag);
         if (!ok) break;
@@ -453,7 +464,7 @@ mla_decode_kernel(const Params p) {
         const float x0 = grp == 0 ? sc[c] : sc[kTile / 2 + c], x1 = grp == 0 ? sc[c + 1] : sc[kTile / 2 + c + 1];
         // sparse: while no entry has been present m_ref is -inf and every logit is -inf: the weights are 0, not NaN
         const float m_use = (SPARSE && m_ref == -INFINITY) ? 0.f : m_ref;
-        const float p0 = exp2f(x0 - m_use), p1 = exp2f(x1 - m_use);
+        const float p0 = ex2_approx(fmaf(x0, post, -m_use)), p1 = ex2_approx(fmaf(x1, post, -m_use));
         s4[(c >> 1) & 3] += p0 + p1;
         split_bf16x2(p0, p1, hi[c >> 1], lo[c >> 1]);
       }
