@@ -432,45 +432,29 @@ push_return_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(peer_bases[src]) +
                                                           returned_offset(world, capacity, hidden, top_k)) +
                          (size_t(me) * capacity + slot) * hidden;
-    // Four column chunks of the row per pass, all their loads issued before the first add, so that a thread has
-    // up to 4 x n 16-byte loads and then four 16-byte peer stores in flight; the adds stay in slot order.
-    constexpr int kChunks = 4;
-    const int stride = blockDim.x * 8;
-    for (int col0 = threadIdx.x * 8; col0 < hidden; col0 += kChunks * stride) {
-      float acc[kChunks][8];
+    for (int col = threadIdx.x * 8; col < hidden; col += blockDim.x * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s0 = 0; s0 < n; s0 += 4) {          // four loads in flight, added in slot order
+        uint4 raw[4];
 #pragma unroll
-      for (int k = 0; k < kChunks; ++k)
+        for (int j = 0; j < 4; ++j)
+          raw[j] = s0 + j < n ? __ldcs(reinterpret_cast<const uint4*>(y + size_t(rows_of[s0 + j]) * hidden + col)) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[k][i] = 0.f;
-      for (int s = 0; s < n; ++s) {
-        const __nv_bfloat16* src_row = y + size_t(rows_of[s]) * hidden;
-        uint4 raw[kChunks];
-#pragma unroll
-        for (int k = 0; k < kChunks; ++k) {
-          const int col = col0 + k * stride;
-          raw[k] = col < hidden ? __ldcs(reinterpret_cast<const uint4*>(src_row + col)) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < kChunks; ++k) {
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+        for (int j = 0; j < 4; ++j) {
+          if (s0 + j >= n) break;
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float2 f = __bfloat1622float2(h[i]);
-            acc[k][2 * i] += f.x;
-            acc[k][2 * i + 1] += f.y;
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
           }
         }
       }
-#pragma unroll
-      for (int k = 0; k < kChunks; ++k) {
-        const int col = col0 + k * stride;
-        if (col < hidden) {
-          uint4 o;
-          o.x = pack_bf16x2(acc[k][0], acc[k][1]); o.y = pack_bf16x2(acc[k][2], acc[k][3]);
-          o.z = pack_bf16x2(acc[k][4], acc[k][5]); o.w = pack_bf16x2(acc[k][6], acc[k][7]);
-          *reinterpret_cast<uint4*>(dst + col) = o;
-        }
-      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(dst + col) = o;
     }
   }
   publish_when_last(sc.done + 1, peer_bases, world, me, *sc.epoch, nullptr, 0, 128 * sizeof(int));
