@@ -108,6 +108,31 @@ class ClockSampler:
                 "samples": len(sm), "samples_under_load": len(loaded), "power_w_max": top}
 
 
+HOST_BINDING = {"cpus": None}
+
+
+def bind_host_to_gpu(local: int):
+    """Keeps this rank's host threads, and with them the pinned buffers they allocate and touch first, on the CPU
+    socket the rank's GPU hangs off: with one rank per GPU and every rank's pinned memory on the socket the launcher
+    happened to start it on, the end-to-end copies of several ranks share one inter-socket link.  Returns the CPU
+    list used, or None where the platform does not tell (then nothing is changed)."""
+    try:
+        props = torch.cuda.get_device_properties(local)
+        address = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        text = Path(f"/sys/bus/pci/devices/{address}/local_cpulist").read_text().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return text
+    except Exception:                                   # noqa: BLE001 - an optimisation only; never fatal
+        return None
+
+
 def dist_setup(n_gpus: int):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -115,6 +140,7 @@ def dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local)
+        HOST_BINDING["cpus"] = bind_host_to_gpu(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     elif n_gpus > 1:
         raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
@@ -812,6 +838,7 @@ def main():
         line["config"]["exchange"] = ("rows written into the owner's memory over NVLink by this library's kernels" if r["exchange"] == "push"
                                       else "NCCL all-to-all, equal splits")
         line["ep_parity"] = r["ep_parity"]
+        line["config"]["host_cpus_rank0"] = HOST_BINDING["cpus"] or "as started"
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
