@@ -266,6 +266,7 @@ struct PushScratch {       // ints in the rank's own (non-symmetric) scratch, af
   int* row_src;            // [rows] source rank of compacted row c
   int* row_slot;           // [rows] its slot in that rank's block
   int* slot_of;            // [T, world]
+  long long wait_clocks;   // budget of a wait for another rank (set at launch: the default, or the test hook's)
 };
 
 // One CTA of 1024 threads per destination rank: slots of the tokens that rank needs, in token order (a block-wide
@@ -352,12 +353,12 @@ push_dispatch_kernel(const uint8_t* __restrict__ hidden_states, const float* __r
 constexpr long long kPeerWaitClockBudget = 20000000000LL;
 
 __device__ __forceinline__ void wait_for_sources(const int* flags, const int* counts, int world, int epoch, int* status,
-                                                 int* cnt /* shared [kMaxWorld] */) {
+                                                 long long budget, int* cnt /* shared [kMaxWorld] */) {
   if (threadIdx.x < world) {
     const long long start = clock64();
     bool ok = true;
     while (ld_acquire_sys(flags + threadIdx.x) < epoch) {
-      if (clock64() - start > kPeerWaitClockBudget) { ok = false; if (status) atomicCAS(status, 0, kStatusWaitFlag); break; }
+      if (clock64() - start > budget) { ok = false; if (status) atomicCAS(status, 0, kStatusWaitFlag); break; }
       __nanosleep(64);
     }
     cnt[threadIdx.x] = ok && counts ? counts[threadIdx.x] : 0;
@@ -375,7 +376,7 @@ push_unpack_kernel(const uint8_t* __restrict__ own_base, PushScratch sc, uint8_t
   __shared__ int pre[kMaxWorld + 1];
   const int lane = threadIdx.x & 31;
   const int epoch = *sc.epoch;
-  wait_for_sources(reinterpret_cast<const int*>(own_base), reinterpret_cast<const int*>(own_base) + 64, world, epoch, sc.status, cnt);
+  wait_for_sources(reinterpret_cast<const int*>(own_base), reinterpret_cast<const int*>(own_base) + 64, world, epoch, sc.status, sc.wait_clocks, cnt);
   if (threadIdx.x == 0) {
     int run = 0;
     for (int r = 0; r < world; ++r) { pre[r] = run; run += min(cnt[r], capacity); }
@@ -467,7 +468,7 @@ push_reduce_kernel(const uint8_t* __restrict__ own_base, PushScratch sc, __nv_bf
                    int hidden, int top_k) {
   __shared__ int cnt[kMaxWorld];
   __shared__ int slots[kMaxWorld];
-  wait_for_sources(reinterpret_cast<const int*>(own_base) + 128, nullptr, world, *sc.epoch, sc.status, cnt);
+  wait_for_sources(reinterpret_cast<const int*>(own_base) + 128, nullptr, world, *sc.epoch, sc.status, sc.wait_clocks, cnt);
   const int t = blockIdx.x;
   if (threadIdx.x < world) slots[threadIdx.x] = sc.slot_of[size_t(t) * world + threadIdx.x];
   __syncthreads();
@@ -573,28 +574,31 @@ extern "C" int cake_b200_ep_push_launch_stage(void* handle, int stage, void* cud
   auto* scale = static_cast<const float*>(h->b[3]);
   auto* peers = static_cast<const unsigned long long*>(h->b[4]);
   auto* own = static_cast<const uint8_t*>(h->b[5]);
+  ep::PushScratch scratch = h->sc;
+  const int hook_kiloclocks = test_hooks().budget_kiloclocks;          // failure-path tests shorten the waits
+  scratch.wait_clocks = hook_kiloclocks > 0 ? (long long)hook_kiloclocks << 10 : ep::kPeerWaitClockBudget;
   switch (stage) {
     case 0: {  // plan + dispatch: this rank's rows go into their owners' receive blocks
-      ep::push_plan_kernel<<<c.world, 1024, 0, s>>>(ids, h->sc, tokens, c.top_k, c.world, c.experts / c.world);
+      ep::push_plan_kernel<<<c.world, 1024, 0, s>>>(ids, scratch, tokens, c.top_k, c.world, c.experts / c.world);
       const int blocks = tokens > 0 ? (tokens * c.world + 7) / 8 : 1;
-      ep::push_dispatch_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(hidden, scale, ids, weights, h->sc, peers, tokens, c.top_k,
+      ep::push_dispatch_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(hidden, scale, ids, weights, scratch, peers, tokens, c.top_k,
                                                                            c.world, c.rank, cap, c.hidden);
       break;
     }
     case 1: {  // wait for every source, then compact the received rows into the rank-local layer's inputs
       const int blocks = (rows + 7) / 8;
-      ep::push_unpack_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(own, h->sc, static_cast<uint8_t*>(h->b[7]),
+      ep::push_unpack_kernel<<<blocks < 1184 ? blocks : 1184, 256, 0, s>>>(own, scratch, static_cast<uint8_t*>(h->b[7]),
                                                                          static_cast<float*>(h->b[8]), static_cast<int*>(h->b[9]),
                                                                          static_cast<float*>(h->b[10]), rows, c.top_k, c.world, cap, c.hidden);
       break;
     }
     case 2:    // combine the local contributions of every received row and write it back to the token's owner
-      ep::push_return_kernel<<<rows, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(h->b[11]), static_cast<const int*>(h->b[12]), h->sc,
+      ep::push_return_kernel<<<rows, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(h->b[11]), static_cast<const int*>(h->b[12]), scratch,
                                                   peers, c.world, c.rank, cap, c.hidden, c.top_k);
       break;
     case 3:    // wait for every rank's partial rows, then add them in rank order
       if (tokens > 0)
-        ep::push_reduce_kernel<<<tokens, 256, 0, s>>>(own, h->sc, static_cast<__nv_bfloat16*>(h->b[13]), c.world, cap, c.hidden, c.top_k);
+        ep::push_reduce_kernel<<<tokens, 256, 0, s>>>(own, scratch, static_cast<__nv_bfloat16*>(h->b[13]), c.world, cap, c.hidden, c.top_k);
       break;
     default:
       return kErrBadArgument;

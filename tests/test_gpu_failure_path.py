@@ -51,3 +51,50 @@ def test_mla_decode_wait_runs_out_and_the_handle_stays_usable(hooks):
     want = attention.paged_decode_reference(cpu, mla=True, page_size=64, per_head_loop=False)
     assert compare.compare(out, want["output"], atol=2.0 ** -16, rtol=2.0 ** -7)[0]
     assert compare.compare(lse, want["lse"], atol=1e-4, rtol=1e-5, ieee=True)[0]
+
+
+def test_push_exchange_wait_for_a_rank_that_never_arrives_runs_out(hooks):
+    """Two ranks of the push exchange live on this GPU (ordinary buffers in place of the symmetric ones); only rank 0
+    runs its step, so the flag it waits for is one that nothing sets.  With the wait budget shortened the wait runs
+    out in about a millisecond, the kernel returns, the status word says so, and the context stays usable: two
+    fresh ranks then complete steps in lock step with the right result."""
+    from open_cake_ir_b200 import ep
+    shape, tokens, world = dict(hidden=1024, inter=512, experts=32), 256, 2
+
+    def make_ranks():
+        sym = ep.PushExpertParallelMoe.symmetric_bytes(tokens // world, shape["hidden"], 8, world, shape["experts"])
+        buffers = [torch.zeros(sym + 256, dtype=torch.uint8, device="cuda") for _ in range(world)]
+        ranks = []
+        for rank in range(world):
+            dev = cake.workloads.moe_inputs(tokens=tokens // world, **shape, local_experts=shape["experts"] // world,
+                                            local_offset=rank * shape["experts"] // world, routing="softmax", device="cuda",
+                                            gen_device="cpu", first_token=rank * tokens // world, total_tokens=tokens)
+            ranks.append(ep.PushExpertParallelMoe(dev, dev["routing_logits"], dev["routing_bias"], dev["hidden_states"],
+                                                  dev["hidden_states_scale"], experts=shape["experts"], routing="softmax",
+                                                  virtual=(rank, world, buffers)))
+        return ranks
+
+    lonely = make_ranks()
+    assert hooks(2048, 0) == 0                 # waits for another rank give up after 2 Mi clocks
+    parts = lonely[0]._parts()
+    parts[0]()                                 # rank 0 routes, plans and pushes its rows ...
+    parts[1]()                                 # ... and waits for rank 1's rows, which never come
+    torch.cuda.synchronize()
+    assert lonely[0].status() == 5 and lonely[1].status() == 0
+    assert hooks(0, 0) == 0
+    for layer in lonely:
+        layer.close()
+
+    ranks = make_ranks()
+    whole = cake.workloads.moe_inputs(tokens=tokens, **shape, local_experts=shape["experts"], local_offset=0,
+                                      routing="softmax", device="cuda", gen_device="cpu")
+    want = cake.fp8_moe(whole, experts=shape["experts"], routing="softmax", act_mode="fp8")
+    for _ in range(2):
+        step_parts = [layer._parts() for layer in ranks]
+        for i in range(len(step_parts[0])):
+            for rank_parts in step_parts:
+                rank_parts[i]()
+        torch.cuda.synchronize()
+        got = torch.cat([layer.output for layer in ranks])
+        assert all(layer.status() == 0 for layer in ranks)
+        assert compare.rel_frobenius(got.cpu(), want.cpu()) <= 1e-2
