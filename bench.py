@@ -674,6 +674,82 @@ def per_gpu_operators(peaks, with_cpu=True):
         row["cpu_baseline"] = {"value": sample_tokens * 1152 / seconds / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                                "sample": f"the first {n} of 32 sequences ({sample_tokens} tokens), fp64 oracle (oracle/attention.py), {runs} run(s)"}
     rows.append(row)
+    rows.extend(next_operators(peaks))
+    return rows
+
+
+def next_operators(peaks):
+    """The operators next to the headline path (two-output add-RMSNorm is timed above): the DeepSeek-V4 gate and
+    indexer top-k, the sparse MLA decode and the causal-prefill forms, at their contracts' shapes or, for prefill, a
+    chunk of the size the reference's cases use.  They are microsecond kernels over data that fits in L2, so the
+    rows give time and algorithmic GB/s and name the bound as latency; parity is the tests' business."""
+    import open_cake_ir_b200 as cake
+    rows = []
+    g = torch.Generator(device="cuda").manual_seed(7)
+
+    def add(name, workload, op, nbytes):
+        ms, stats, launches = time_rotating([op.launch])
+        status = op.status() if hasattr(op, "status") else 0
+        rows.append({"operator": name, "workload": workload, "ms": ms, "samples": stats, "launches_timed": launches,
+                     "bound": "latency", "unit": "GB/s", "achieved": nbytes / ms / 1e6, "peak": peaks["hbm_gbs"],
+                     "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"], "status": status,
+                     "l2": "one buffer set that fits in L2: a latency-bound kernel, timed back to back"})
+
+    tokens, experts, top_k = 4096, 384, 6
+    logits = torch.randn((tokens, experts), generator=g, device="cuda") * 2
+    bias = torch.rand(experts, generator=g, device="cuda") * 0.5
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device="cuda")
+    ids = torch.empty((tokens, top_k), dtype=torch.int32, device="cuda")
+    add("v4_moe_gate", f"router_logits fp32 [{tokens},{experts}], top {top_k}", cake.V4MoeGate(logits, bias, weights, ids, top_k=top_k, route_scale=2.5),
+        logits.numel() * 4 + experts * 4 + 2 * tokens * top_k * 4)
+
+    rows_q, candidates, keep = 512, 2048, 1024
+    scores = torch.randn((rows_q, candidates), generator=g, device="cuda")
+    indices = torch.empty((rows_q, keep), dtype=torch.int32, device="cuda")
+    add("csa_topk", f"index_scores fp32 [{rows_q},{candidates}] -> top {keep}", cake.CsaTopk(scores, indices), scores.numel() * 4 + indices.numel() * 4)
+
+    t, heads, pages, page, listed = 64, 16, 512, 64, 2048
+    q_nope = (torch.rand((t, heads, 512), generator=g, device="cuda") - 0.5).to(torch.bfloat16)
+    q_pe = (torch.rand((t, heads, 64), generator=g, device="cuda") - 0.5).to(torch.bfloat16)
+    ckv = torch.randn((pages, page, 512), generator=g, device="cuda").to(torch.bfloat16)
+    kpe = torch.randn((pages, page, 64), generator=g, device="cuda").to(torch.bfloat16)
+    sparse = torch.stack([torch.randperm(pages * page, generator=g, device="cuda")[:listed] for _ in range(t)]).to(torch.int32)
+    out = torch.empty_like(q_nope)
+    add("sparse_mla_decode", f"{t} query rows, {heads} heads, {listed} listed cache rows each (page {page})",
+        cake.SparseMlaDecode(q_nope, q_pe, ckv, kpe, sparse, out), t * listed * 1152 + 2 * q_nope.numel() * 2 + q_pe.numel() * 2 + sparse.numel() * 4)
+
+    segments, q_len, kv_len, hq, hkv = 4, 32, 512, 32, 8
+    page = 16
+    total_q, pages_per = segments * q_len, kv_len // page
+    q = (torch.rand((total_q, hq, 128), generator=g, device="cuda") - 0.5).to(torch.bfloat16)
+    k = torch.randn((segments * pages_per, page, hkv, 128), generator=g, device="cuda").to(torch.bfloat16)
+    v = torch.randn((segments * pages_per, page, hkv, 128), generator=g, device="cuda").to(torch.bfloat16)
+    qo = torch.arange(0, total_q + 1, q_len, dtype=torch.int32, device="cuda")
+    kvp = torch.arange(0, segments * pages_per + 1, pages_per, dtype=torch.int32, device="cuda")
+    kv_indices = torch.arange(segments * pages_per, dtype=torch.int32, device="cuda")
+    last = torch.full((segments,), page, dtype=torch.int32, device="cuda")
+    scale = torch.tensor([128 ** -0.5], device="cuda")
+    o = torch.empty_like(q)
+    lse = torch.empty((total_q, hq), dtype=torch.float32, device="cuda")
+    add("gqa_causal_prefill_paged", f"{segments} segments x {q_len} query rows over {kv_len} KV rows, {hq}/{hkv} heads, page {page}",
+        cake.GqaCausalPrefill(q, k, v, qo, kvp, kv_indices, last, scale, o, lse, max_kv_len=kv_len),
+        2 * k.numel() * 2 + 2 * q.numel() * 2 + lse.numel() * 4)
+
+    heads, page = 16, 64
+    pages_per = kv_len // page
+    qn = (torch.rand((total_q, heads, 512), generator=g, device="cuda") - 0.5).to(torch.bfloat16)
+    qp = (torch.rand((total_q, heads, 64), generator=g, device="cuda") - 0.5).to(torch.bfloat16)
+    ckv2 = torch.randn((segments * pages_per, page, 512), generator=g, device="cuda").to(torch.bfloat16)
+    kpe2 = torch.randn((segments * pages_per, page, 64), generator=g, device="cuda").to(torch.bfloat16)
+    kvp2 = torch.arange(0, segments * pages_per + 1, pages_per, dtype=torch.int32, device="cuda")
+    idx2 = torch.arange(segments * pages_per, dtype=torch.int32, device="cuda")
+    last2 = torch.full((segments,), page, dtype=torch.int32, device="cuda")
+    scale2 = torch.tensor([0.1352337788608801], device="cuda")
+    o2 = torch.empty_like(qn)
+    lse2 = torch.empty((total_q, heads), dtype=torch.float32, device="cuda")
+    add("mla_causal_prefill_paged", f"{segments} segments x {q_len} query rows over {kv_len} latent rows, {heads} heads, page {page}",
+        cake.MlaCausalPrefill(qn, qp, ckv2, kpe2, qo, kvp2, idx2, last2, scale2, o2, lse2, max_kv_len=kv_len),
+        segments * kv_len * 1152 + 2 * qn.numel() * 2 + qp.numel() * 2 + lse2.numel() * 4)
     return rows
 
 
